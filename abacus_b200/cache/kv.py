@@ -32,6 +32,7 @@ class LayerKV:
     ring_pages: int
     tokens_per_page: int
     window: object
+    pinned_pages: int = 0  # a windowed group that also keeps a sequence's first pages (they come before the ring)
 
 
 @dataclass
@@ -39,6 +40,7 @@ class EntryView:
     owns_storage: bool  # False: the entry reads the cache of another entry
     kv: object  # LayerKV or None
     state: object  # float32 [slots, *state_shape] or None
+    states: dict = None  # further states by name, [slots, *shape] each
 
 
 class _Group:
@@ -46,25 +48,30 @@ class _Group:
         tpp = TOKENS_PER_PAGE
         self.need, self.entries = need, entries
         self.ring_pages = 0 if need.window is None else (need.window + tpp - 2) // tpp + 1
+        self.pinned_pages = -(-need.keep_first // tpp) if self.ring_pages else 0
         per_seq = -(-max_context // tpp)
         if self.ring_pages:
-            per_seq = min(per_seq, self.ring_pages)
-            n_pages = min(n_pages, max_slots * self.ring_pages)
+            per_seq = min(per_seq, self.pinned_pages + self.ring_pages)
+            n_pages = min(n_pages, max_slots * (self.pinned_pages + self.ring_pages))
         self.table_width = max(1, min(per_seq, n_pages))
-        self.book = PageBook(n_pages, tpp, self.ring_pages)
+        self.book = PageBook(n_pages, tpp, self.ring_pages, self.pinned_pages)
         shape = (len(entries), n_pages, need.n_kv_heads, tpp, need.head_dim)
         self.k = guards.zeros(shape, dtype, device, what="cache keys")  # guard words around the pools
-        self.v = guards.zeros(shape, dtype, device, what="cache values")
+        self.v = guards.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype, device, what="cache values")
         # pageable on purpose: a copy from pageable memory is staged before copy_ returns, so the
         # host may rewrite a row (a slot used again) while earlier steps are still in flight
         self.table_host = torch.zeros((max_slots, self.table_width), dtype=torch.int32)
         self.table = torch.zeros((max_slots, self.table_width), dtype=torch.int32, device=device)
 
 
-class SequenceCache:
-    """needs: one CacheNeed (or None) per schedule entry; sources: per entry, None or the entry it reads."""
+_STATE_TYPES = {"float32": torch.float32, "int32": torch.int32}
 
-    def __init__(self, needs, sources, max_tokens, dtype, device, max_slots=None, max_context=None):
+
+class SequenceCache:
+    """needs: one CacheNeed (or None) per schedule entry; sources: per entry, None or the entry it reads.
+    frame_need: what the model's frame keeps per sequence (a CacheNeed with states only), or None."""
+
+    def __init__(self, needs, sources, max_tokens, dtype, device, max_slots=None, max_context=None, frame_need=None):
         tpp = TOKENS_PER_PAGE
         self.device, self.dtype = torch.device(device), dtype
         self.n_pages = max(1, -(-max_tokens // tpp))
@@ -72,33 +79,47 @@ class SequenceCache:
         self.max_context = min(max_context or self.n_pages * tpp, self.n_pages * tpp)
         self.slots = FreeList(self.max_slots, "cache slot")
         self.length = {}
-        self.groups, self._of_entry, self.states = [], {}, {}
+        self.groups, self._of_entry, self.states, self.named_states = [], {}, {}, {}
         by_need = {}
         for e, (need, source) in enumerate(zip(needs, sources)):
             if source is not None or need is None:
                 continue
             if need.n_kv_heads > 0:
-                key = (need.n_kv_heads, need.head_dim, need.window)
+                keep_first = need.keep_first if need.window is not None else 0
+                key = (need.n_kv_heads, need.head_dim, need.window, need.v_head_dim or need.head_dim, keep_first)
                 by_need.setdefault(key, []).append(e)
             if need.state_shape:
                 self.states[e] = guards.zeros((self.max_slots, *need.state_shape), torch.float32, device,
                                               what=f"state of entry {e}")
-        for (hkv, hd, window), entries in by_need.items():
-            g = _Group(CacheNeed(hkv, hd, window), entries, self.n_pages, self.max_slots, self.max_context, dtype,
-                       self.device)
+            if need.states:
+                self.named_states[e] = self._named(need, f"entry {e}")
+        self.frame = EntryView(True, None, None, self._named(frame_need, "the frame") if frame_need is not None else {})
+        for (hkv, hd, window, vd, keep_first), entries in by_need.items():
+            g = _Group(CacheNeed(hkv, hd, window, v_head_dim=vd, keep_first=keep_first), entries, self.n_pages,
+                       self.max_slots, self.max_context, dtype, self.device)
             self.groups.append(g)
             for i, e in enumerate(entries):
                 self._of_entry[e] = (g, i)
         self.sources = list(sources)
         self.views = [self._view(e) for e in range(len(needs))]
 
+    def _named(self, need, whose):
+        return {name: guards.zeros((self.max_slots, *shape), _STATE_TYPES[kind], self.device,
+                                   what=f"state {name} of {whose}") for name, shape, kind in need.states}
+
+    def _all_states(self):
+        yield from self.states.values()
+        for named in list(self.named_states.values()) + [self.frame.states]:
+            yield from named.values()
+
     def _view(self, e):
         owner = e if self.sources[e] is None else self.sources[e]
         kv = None
         if owner in self._of_entry:
             g, i = self._of_entry[owner]
-            kv = LayerKV(g.k[i], g.v[i], g.table, g.table_width, g.ring_pages, TOKENS_PER_PAGE, g.need.window)
-        return EntryView(self.sources[e] is None, kv, self.states.get(owner))
+            kv = LayerKV(g.k[i], g.v[i], g.table, g.table_width, g.ring_pages, TOKENS_PER_PAGE, g.need.window,
+                         g.pinned_pages)
+        return EntryView(self.sources[e] is None, kv, self.states.get(owner), self.named_states.get(owner, {}))
 
     # ------------------------------------------------------------ slots
     def open_slot(self):
@@ -107,7 +128,7 @@ class SequenceCache:
         self.length[slot] = 0
         for g in self.groups:
             g.book.open(slot)
-        for state in self.states.values():
+        for state in self._all_states():
             state[slot].zero_()
         return slot
 
@@ -156,6 +177,17 @@ class SequenceCache:
         for slot, new_length in wanted:
             self.reserve(slot, new_length)
 
+    def save_states(self, slots):
+        """Copies of every per-sequence state of these slots (of the mixers' and of the frame's), for restore_states.
+        Keys and values need none: writing a position twice leaves the same bytes, running a recurrence twice does not."""
+        index = torch.tensor(list(slots), dtype=torch.int64, device=self.device)
+        return index, [state.index_select(0, index) for state in self._all_states()]
+
+    def restore_states(self, saved):
+        index, copies = saved
+        for state, copy in zip(self._all_states(), copies):
+            state.index_copy_(0, index, copy)
+
     def advance(self, slot, n_new):
         self.length[slot] += n_new
 
@@ -164,5 +196,5 @@ class SequenceCache:
         return min((g.book.pages.n_free for g in self.groups), default=0)
 
     def bytes(self):
-        total = sum(2 * g.k.numel() * g.k.element_size() for g in self.groups)
-        return total + sum(s.numel() * 4 for s in self.states.values())
+        total = sum((g.k.numel() + g.v.numel()) * g.k.element_size() for g in self.groups)
+        return total + sum(s.numel() * 4 for s in self._all_states())

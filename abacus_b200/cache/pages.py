@@ -45,11 +45,13 @@ class PageBook:
     """The pages of one cache group: per slot, the list of pages that hold its tokens.
 
     A group with ring_pages > 0 keeps at most that many pages per slot; position p
-    lives in logical page (p // tokens_per_page) % ring_pages.
+    lives in logical page (p // tokens_per_page) % ring_pages. With pinned_pages the slot's first
+    pinned_pages pages stay and the ring comes after them (pinned_pages + ring_pages at most).
     """
 
-    def __init__(self, n_pages, tokens_per_page, ring_pages=0):
+    def __init__(self, n_pages, tokens_per_page, ring_pages=0, pinned_pages=0):
         self.tokens_per_page, self.ring_pages = tokens_per_page, ring_pages
+        self.pinned_pages = pinned_pages if ring_pages else 0
         self.pages = FreeList(n_pages, "cache page")
         self.of_slot = {}
 
@@ -60,7 +62,7 @@ class PageBook:
 
     def pages_for(self, length):
         n = -(-length // self.tokens_per_page)
-        return min(n, self.ring_pages) if self.ring_pages else n
+        return min(n, self.pinned_pages + self.ring_pages) if self.ring_pages else n
 
     def grow(self, slot, length):
         """Make room for `length` tokens in all; returns [(logical index, page)] newly added."""

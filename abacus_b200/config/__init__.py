@@ -2,7 +2,8 @@ from .registry import (ConfigError, architecture_names, architecture_of, get_arc
                        read_config_json, register_architecture)
 from .specs import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, NormSpec, RotarySpec, ScheduleEntry)
 from .qwen3 import Qwen3Config
+from .temetar import TemetarConfig
 
 __all__ = ["ConfigError", "architecture_names", "architecture_of", "get_architecture", "load_config",
            "read_config_json", "register_architecture", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
-           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config"]
+           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig"]

@@ -55,9 +55,13 @@ def read_config_json(folder):
 
 
 def architecture_of(raw):
+    """By config.json's "architectures" (a list, its first entry) or "architecture" (one name)."""
     names = raw.get("architectures")
+    if names is None and isinstance(raw.get("architecture"), str):
+        names = [raw["architecture"]]
     if not names or not isinstance(names, list):
-        raise ConfigError('config.json has no "architectures" list; known: ' + ", ".join(architecture_names()))
+        raise ConfigError('config.json has neither an "architectures" list nor an "architecture" name; known: '
+                          + ", ".join(architecture_names()))
     return get_architecture(names[0])
 
 

@@ -15,9 +15,13 @@ from typing import Optional
 
 @dataclass(frozen=True)
 class NormSpec:
-    """RMSNorm as src/model.c:164-169: w * (x / sqrt(mean(x^2) + eps))."""
+    """RMSNorm as src/model.c:164-169: w * (x / sqrt(mean(x^2) + eps)).
+
+    one_plus: the checkpoint stores the weight around zero and the norm multiplies by 1 + w.
+    """
     size: int
     eps: float
+    one_plus: bool = False
     kind: str = "rmsnorm"
 
 
@@ -40,6 +44,10 @@ class AttentionSpec:
 
     window None: every earlier key; W: the last W keys, the token's own included.
     scale multiplies the scores (src/model.c:202 uses 1/sqrt(head_dim)).
+    v_head_dim: the size of a value head where it is not head_dim. keep_first F (with a window): the
+    sequence's first F keys stay visible behind the window, at their true positions. sink: a learned score
+    per query head (slot "sink") that joins the softmax's denominator once, unscaled, with no key and no value.
+    exact_weights: the softmax's weights stay float32 in the second product also where the model is bfloat16.
     """
     hidden: int
     n_heads: int
@@ -49,7 +57,36 @@ class AttentionSpec:
     qk_norm_eps: Optional[float]  # None: no per-head norm of q and k
     position: Optional[RotarySpec]
     window: Optional[int] = None
+    v_head_dim: Optional[int] = None
+    keep_first: int = 0
+    sink: bool = False
+    exact_weights: bool = False
     kind: str = "attention"
+
+
+@dataclass(frozen=True)
+class DeltaRuleSpec:
+    """A recurrent mixer: the gated delta rule with a decay per head and key channel.
+
+    Per head a state S [key_dim, value_dim] (float32, zero at a sequence's start):
+        S <- diag(g) S;  e = b (v - S^T k);  S <- S + k e^T;  o = S^T q
+    q, k (n_kv_heads x key_dim; head h uses q/k head h // (n_heads / n_kv_heads)) and v (n_heads x value_dim) each
+    pass a causal convolution of conv_taps taps per channel and SiLU; q and k are then unit vectors per head
+    (x / sqrt(sum x^2 + unit_eps)), q times key_dim^-1/2. b = sigmoid(.) per head. g = exp(-exp(A_h) *
+    softplus(W2 (W1 x) + bias)), decay_rank the inner size of that pair of matrices. o is normed per head over
+    value_dim (eps norm_eps, a weight shared by the heads) and gated by sigmoid(G2 (G1 x)), gate_rank the inner size.
+    """
+    hidden: int
+    n_heads: int
+    n_kv_heads: int
+    key_dim: int
+    value_dim: int
+    conv_taps: int
+    decay_rank: int
+    gate_rank: int
+    norm_eps: float
+    unit_eps: float = 1e-6
+    kind: str = "channel_delta"
 
 
 @dataclass(frozen=True)
@@ -79,6 +116,37 @@ class BlockSpec:
 
 
 @dataclass(frozen=True)
+class StreamsBlockSpec:
+    """One layer over a residual stream that is kept as `streams` copies X[0..s) with learned connections.
+
+    For each branch (the mixer, then the feed-forward; ffn None: the mixer alone) with its connection
+    (enter [s], mix [s, s] indexed [from, to], leave [s]):
+        u = sum_s enter[s] X[s];  y = branch(norm(u));  X'[t] = sum_s mix[s, t] X[s] + branch_scale * leave[t] * y
+    learned False: no connection tensors; enter = mix = leave = 1 (one stream: x += branch_scale * y).
+    """
+    mixer_norm: object
+    mixer: object
+    ffn_norm: object
+    ffn: object
+    streams: int = 1
+    branch_scale: float = 1.0
+    learned: bool = True
+    kind: str = "streams_pre_norm"
+
+
+@dataclass(frozen=True)
+class PairEmbeddingSpec:
+    """The frame "scaled_pairs": x = table[token] * scale, plus, with buckets > 0, row
+    (previous token * mul_prev + token * mul_cur) mod buckets of a second table (a sequence's first token: row
+    `buckets`, the last). The stream starts as `streams` copies of x and ends as their sum, normed."""
+    scale: float = 1.0
+    buckets: int = 0
+    mul_prev: int = 0
+    mul_cur: int = 0
+    streams: int = 1
+
+
+@dataclass(frozen=True)
 class ScheduleEntry:
     """One entry of the run order.
 
@@ -102,6 +170,7 @@ class ModelSpec:
     max_positions: int
     stop_tokens: tuple = field(default_factory=tuple)
     frame: str = "plain"  # how tokens become the stream and the stream logits (parts/frame.py)
+    frame_spec: object = None  # what that frame needs beyond the sizes above
 
     @property
     def kind(self):  # the frame is built from the model's spec

@@ -2,7 +2,10 @@
 // multiple of 8, any number of heads and groups, with or without a window. One block per
 // (token, query head); float32 arithmetic with an online softmax over tiles of 128 keys (in the
 // bfloat16 instantiation the probabilities are rounded to bfloat16 for the second product, as in
-// the tensor-core kernels, and summed unrounded).
+// the tensor-core kernels, and summed unrounded; a model that wants them in float32 says so).
+// Options: values of another size than keys; a window that also keeps a sequence's first keys (key j is
+// seen from i when j <= i and (i - j < window or j < keep_first)); a sink, a learned score per head that
+// joins the softmax's denominator once, unscaled, without a key or a value.
 // It serves prefill and decode alike and is the kernel every size falls back to; the float32
 // path of the model uses nothing else for attention.
 //
@@ -21,8 +24,11 @@ struct AttnGeneric {
     long long q_row;    // elements between rows of q
     void *out;          // [tokens, n_heads * head_dim]
     int n_heads, n_kv_heads, head_dim;
+    int v_dim;          // size of a value head (out is [tokens, n_heads * v_dim])
     float scale;
     int window;         // 0: all earlier keys
+    int keep_first;     // with a window: the sequence's first keep_first keys are seen too
+    const float *sink;  // [n_heads] or null
     const int *token_seq, *token_pos, *seq_slot, *seq_start, *seq_pos0;
     // keys and values either in the paged cache ...
     const void *k_pool, *v_pool;
@@ -31,6 +37,7 @@ struct AttnGeneric {
     // row seq_start[s] + j - seq_pos0[s]
     const void *k_step, *v_step;
     long long kv_row;   // elements between rows of k_step / v_step
+    PagedCache v_cache; // the values' pool has pages of v_dim
 };
 
 template <typename T> __device__ __forceinline__ float dot_row(const float *q, const T *k, int hd);
@@ -57,42 +64,48 @@ template <> __device__ __forceinline__ float dot_row<__nv_bfloat16>(const float 
     return acc;
 }
 
-template <typename T> __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGeneric p) {
+// ROUNDED_P: the probabilities are a stored tensor in the model's type (bfloat16) for the second product.
+template <typename T, bool ROUNDED_P>
+__global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGeneric p) {
     __shared__ float q_s[ATT_MAX_HEAD_DIM];
     __shared__ float p_s[ATT_THREADS];
     __shared__ long long v_off[ATT_THREADS];
     __shared__ float scratch[33];
-    constexpr bool ROUNDED_P = sizeof(T) == 2;  // bfloat16: the probabilities are a stored tensor too
-    int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, hd = p.head_dim;
+    int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, hd = p.head_dim, vd = p.v_dim;
     int seq = p.token_seq[t];
-    T *out = (T *)p.out + ((long long)t * p.n_heads + h) * hd;
+    T *out = (T *)p.out + ((long long)t * p.n_heads + h) * vd;
     if (seq < 0) {  // padding
-        for (int d = tid; d < hd; d += ATT_THREADS) out[d] = from_float<T>(0.0f);
+        for (int d = tid; d < vd; d += ATT_THREADS) out[d] = from_float<T>(0.0f);
         return;
     }
     int pos = p.token_pos[t], slot = p.seq_slot[seq];
     int kvh = h / (p.n_heads / p.n_kv_heads);
     int lo = p.window > 0 && pos - p.window + 1 > 0 ? pos - p.window + 1 : 0;
+    // the sequence's first keys that the window no longer reaches: positions [0, first_end)
+    int first_end = p.keep_first < lo ? p.keep_first : lo;
     const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)h * hd;
     for (int d = tid; d < hd; d += ATT_THREADS) q_s[d] = to_float(q[d]);
     __syncthreads();
 
     float m = -INFINITY, l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
-    for (int base = lo; base <= pos; base += ATT_THREADS) {
+    if (p.sink) m = p.sink[h], l = 1.0f;  // a key with this score and no value (never with ROUNDED_P)
+    // two runs of keys: the kept first ones, then the window (or everything up to the token)
+    for (int run = first_end > 0 ? 0 : 1; run < 2; run++)
+    for (int base = run ? lo : 0, end = run ? pos : first_end - 1; base <= end; base += ATT_THREADS) {
         int j = base + tid;
-        bool valid = j <= pos;
+        bool valid = j <= end;
         float s = -INFINITY;
         if (valid) {
             const T *k;
             long long vo;
             if (p.k_step) {
                 long long row = (long long)p.seq_start[seq] + j - p.seq_pos0[seq];
-                vo = row * p.kv_row + (long long)kvh * hd;
-                k = (const T *)p.k_step + vo;
+                vo = row * p.kv_row + (long long)kvh * vd;
+                k = (const T *)p.k_step + row * p.kv_row + (long long)kvh * hd;
             } else {
                 int page = cache_page(p.cache, slot, j);
-                vo = cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
-                k = (const T *)p.k_pool + vo;
+                vo = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, vd);
+                k = (const T *)p.k_pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
             }
             v_off[tid] = vo;
             s = dot_row<T>(q_s, k, hd) * (ROUNDED_P ? p.scale * 1.4426950408889634f : p.scale);
@@ -111,32 +124,39 @@ template <typename T> __global__ void __launch_bounds__(ATT_THREADS) attention_g
         }
         // the probabilities of the second product are a stored tensor: bfloat16 where the model's are (the
         // tensor-core kernels must round them, so every kernel does); the row's sum is of the unrounded ones
-        p_s[tid] = to_float(from_float<T>(pj));
+        p_s[tid] = ROUNDED_P ? to_float(from_float<T>(pj)) : pj;
         l = l * corr + block_sum(pj, scratch);  // the barrier inside also publishes p_s and v_off
         m = m_new;
-        int n_valid = pos - base + 1 < ATT_THREADS ? pos - base + 1 : ATT_THREADS;
+        int n_valid = end - base + 1 < ATT_THREADS ? end - base + 1 : ATT_THREADS;
         const T *v_base = (const T *)(p.k_step ? p.v_step : p.v_pool);
         acc0 *= corr, acc1 *= corr;
-        if (tid < hd) {
+        if (tid < vd) {
             for (int jj = 0; jj < n_valid; jj++) {
                 const T *v = v_base + v_off[jj];
                 acc0 = fmaf(p_s[jj], to_float(v[tid]), acc0);
-                if (tid + ATT_THREADS < hd) acc1 = fmaf(p_s[jj], to_float(v[tid + ATT_THREADS]), acc1);
+                if (tid + ATT_THREADS < vd) acc1 = fmaf(p_s[jj], to_float(v[tid + ATT_THREADS]), acc1);
             }
         }
         __syncthreads();  // p_s and v_off are rewritten by the next tile
     }
-    if (tid < hd) out[tid] = from_float<T>(acc0 / l);
-    if (tid + ATT_THREADS < hd) out[tid + ATT_THREADS] = from_float<T>(acc1 / l);
+    if (tid < vd) out[tid] = from_float<T>(acc0 / l);
+    if (tid + ATT_THREADS < vd) out[tid + ATT_THREADS] = from_float<T>(acc1 / l);
 }
 
-extern "C" int abk_attention_generic(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+extern "C" int abk_attention_general(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
                                      int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
                                      const int *token_pos, const int *seq_slot, const int *seq_start,
                                      const int *seq_pos0, const void *k_pool, const void *v_pool,
                                      const int *page_table, int table_width, int ring_pages, int tokens_per_page,
-                                     const void *k_step, const void *v_step, long long kv_row, void *stream) {
+                                     const void *k_step, const void *v_step, long long kv_row, int v_dim,
+                                     int keep_first, int pinned_pages, const float *sink, int exact_weights,
+                                     void *stream) {
     if (n_tokens <= 0) return 0;
+    if (v_dim <= 0) v_dim = head_dim;
+    if (v_dim > ATT_MAX_HEAD_DIM) ABK_REFUSE("attention: value size %d is more than %d", v_dim, ATT_MAX_HEAD_DIM);
+    if (keep_first < 0 || (keep_first > 0 && window <= 0)) keep_first = 0;
+    if (sink && !exact_weights && dtype == ABK_BF16)
+        ABK_REFUSE("attention: a sink goes with softmax weights in float32 (exact_weights)");
     if (head_dim > ATT_MAX_HEAD_DIM || head_dim % 8 || head_dim < 8)
         ABK_REFUSE("attention: head_dim %d is not a multiple of 8 up to %d", head_dim, ATT_MAX_HEAD_DIM);
     if (n_kv_heads < 1 || n_heads % n_kv_heads)
@@ -148,12 +168,29 @@ extern "C" int abk_attention_generic(const void *q, long long q_row, void *out, 
     p.seq_start = seq_start, p.seq_pos0 = seq_pos0, p.k_pool = k_pool, p.v_pool = v_pool;
     p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
     p.cache.tokens_per_page = tokens_per_page;
+    p.cache.pinned_pages = pinned_pages;
+    p.v_cache = p.cache;
     p.k_step = k_step, p.v_step = v_step, p.kv_row = kv_row;
+    p.v_dim = v_dim, p.keep_first = keep_first, p.sink = sink;
     dim3 grid(n_tokens, n_heads);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dtype == ABK_BF16)
-        attention_generic_kernel<__nv_bfloat16><<<grid, ATT_THREADS, 0, s>>>(p);
+    if (dtype == ABK_BF16 && !exact_weights)
+        attention_generic_kernel<__nv_bfloat16, true><<<grid, ATT_THREADS, 0, s>>>(p);
+    else if (dtype == ABK_BF16)
+        attention_generic_kernel<__nv_bfloat16, false><<<grid, ATT_THREADS, 0, s>>>(p);
     else
-        attention_generic_kernel<float><<<grid, ATT_THREADS, 0, s>>>(p);
+        attention_generic_kernel<float, false><<<grid, ATT_THREADS, 0, s>>>(p);
     return ABK_LAUNCH_RESULT();
+}
+
+// The same without the options: values as large as keys, no kept first keys, no sink, probabilities in the model's type.
+extern "C" int abk_attention_generic(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+                                     int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
+                                     const int *token_pos, const int *seq_slot, const int *seq_start,
+                                     const int *seq_pos0, const void *k_pool, const void *v_pool,
+                                     const int *page_table, int table_width, int ring_pages, int tokens_per_page,
+                                     const void *k_step, const void *v_step, long long kv_row, void *stream) {
+    return abk_attention_general(q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, token_seq,
+                                 token_pos, seq_slot, seq_start, seq_pos0, k_pool, v_pool, page_table, table_width,
+                                 ring_pages, tokens_per_page, k_step, v_step, kv_row, head_dim, 0, 0, nullptr, 0, stream);
 }

@@ -216,16 +216,25 @@ __device__ __forceinline__ float block_max(float v, float *scratch) {
 //   tokens_per_page keys per page; a sequence's pages are listed in its row of the page table.
 //   ring_pages > 0: the sequence keeps only that many pages and position p lives in
 //   logical page (p / tokens_per_page) % ring_pages (a window of the most recent keys).
+//   pinned_pages > 0 (with a ring): the sequence's first pinned_pages pages stay for good (a window that also keeps
+//   the first keys) and the ring comes after them: a later page L lives in pinned + (L - pinned) % ring_pages.
 struct PagedCache {
     const int *page_table;  // [slots, table_width]
     int table_width;
     int ring_pages;         // 0: all pages are kept
     int tokens_per_page;
+    int pinned_pages = 0;
 };
 __device__ __forceinline__ int cache_page(const PagedCache &c, int slot, int pos) {
     int logical = pos / c.tokens_per_page;
-    if (c.ring_pages > 0) logical %= c.ring_pages;
+    if (c.ring_pages > 0 && logical >= c.pinned_pages) logical = c.pinned_pages + (logical - c.pinned_pages) % c.ring_pages;
     return c.page_table[(long long)slot * c.table_width + logical];
+}
+// Whether position pos of a sequence that holds len_after tokens once this step is written still has its place in the
+// cache then (false: a later token of the same step takes the place, so pos is not written).
+__device__ __forceinline__ bool cache_keeps(const PagedCache &c, int pos, int len_after) {
+    if (c.ring_pages <= 0 || pos / c.tokens_per_page < c.pinned_pages) return true;
+    return pos + c.ring_pages * c.tokens_per_page > len_after - 1;
 }
 // Element offset of (page, kv head, position, 0) in a pool laid out [pages, kv heads, tokens_per_page, head_dim].
 __device__ __forceinline__ long long cache_offset(const PagedCache &c, int page, int kv_head, int n_kv_heads, int pos,

@@ -211,6 +211,7 @@ extern "C" int abk_swiglu(const void *gate_up, void *act, int dtype, int n_token
 struct QkvPrep {
     void *qkv;
     int n_heads, n_kv_heads, head_dim;
+    int v_dim = 0;  // size of a value head where it is not head_dim (0: head_dim); the general kernel alone takes it
     int q_only;  // only the q heads are prepared (keys and values come from elsewhere)
     const int *token_seq, *token_pos, *seq_slot, *seq_len_after;
     const float *q_norm, *k_norm;
@@ -235,9 +236,13 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
     if (seq < 0) return;
     int pos = p.token_pos[t];
     int hd = p.head_dim;
-    T *row = (T *)p.qkv + ((long long)t * total_heads + head) * hd;
+    const int vd = p.v_dim > 0 ? p.v_dim : hd;
     bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
     int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
+    // a row of qkv: the q heads and the k heads of head_dim, then the v heads of vd
+    const long long row_size = (long long)(p.n_heads + p.n_kv_heads) * hd + (long long)p.n_kv_heads * vd;
+    T *row = (T *)p.qkv + (long long)t * row_size +
+             (is_q || is_k ? (long long)head * hd : (long long)(p.n_heads + p.n_kv_heads) * hd + (long long)kv_head * vd);
     float *b = buf[warp];
 
     if (is_q || is_k) {
@@ -269,15 +274,13 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
     }
     if (is_q || !p.k_pool) return;
     // A windowed cache keeps ring_pages pages; of the positions that share a place only the last is written.
-    if (p.cache.ring_pages > 0 &&
-        pos + p.cache.ring_pages * p.cache.tokens_per_page <= p.seq_len_after[seq] - 1)
-        return;
+    if (!cache_keeps(p.cache, pos, p.seq_len_after[seq])) return;
     int page = cache_page(p.cache, p.seq_slot[seq], pos);
-    T *dst = (T *)(is_k ? p.k_pool : p.v_pool) + cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, hd);
+    T *dst = (T *)(is_k ? p.k_pool : p.v_pool) + cache_offset(p.cache, page, kv_head, p.n_kv_heads, pos, is_k ? hd : vd);
     if (is_k)
         for (int j = lane; j < hd; j += 32) dst[j] = from_float<T>(b[j]);
     else
-        for (int j = lane; j < hd; j += 32) dst[j] = row[j];
+        for (int j = lane; j < vd; j += 32) dst[j] = row[j];
 }
 
 // The same for bfloat16 heads of 64 * EPH elements that are rotated whole in half pairing (or not at
@@ -440,6 +443,36 @@ template <int HD> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_pr
             for (int u = 0; u < FAST_SLOTS; u++) cur[u] = next[u];
         }
     }
+}
+
+// v_dim: the size of a value head (0: head_dim); pinned_pages: see PagedCache.
+extern "C" int abk_qkv_prep_general(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
+                                    int q_only, const int *token_seq, const int *token_pos, const int *seq_slot,
+                                    const int *seq_len_after, const float *q_norm, const float *k_norm, float eps,
+                                    const float *cos, const float *sin, int rotary_dim, int interleaved, void *k_pool,
+                                    void *v_pool, const int *page_table, int table_width, int ring_pages,
+                                    int tokens_per_page, int v_dim, int pinned_pages, void *stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim > MAX_HEAD_DIM || head_dim < 2 || head_dim % 2)
+        ABK_REFUSE("qkv_prep: head_dim %d is not an even number up to %d", head_dim, MAX_HEAD_DIM);
+    if (cos && (rotary_dim < 2 || rotary_dim % 2 || rotary_dim > head_dim))
+        ABK_REFUSE("qkv_prep: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
+    QkvPrep p;
+    p.qkv = qkv, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.head_dim = head_dim, p.q_only = q_only;
+    p.v_dim = v_dim;
+    p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.seq_len_after = seq_len_after;
+    p.q_norm = q_norm, p.k_norm = k_norm, p.eps = eps, p.cos = cos, p.sin = sin;
+    p.rotary_dim = rotary_dim, p.interleaved = interleaved, p.k_pool = k_pool, p.v_pool = v_pool;
+    p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
+    p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
+    int total_heads = n_heads + 2 * n_kv_heads;
+    dim3 grid(n_tokens, (total_heads + PREP_WARPS - 1) / PREP_WARPS);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16)
+        abk_launch(qkv_prep_kernel<__nv_bfloat16>, grid, dim3(PREP_WARPS * 32), 0, s, p);
+    else
+        abk_launch(qkv_prep_kernel<float>, grid, dim3(PREP_WARPS * 32), 0, s, p);
+    return ABK_LAUNCH_RESULT();
 }
 
 extern "C" int abk_qkv_prep(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim, int q_only,

@@ -1,0 +1,187 @@
+// A residual stream kept as several copies ("streams") with learned connections between them, and the
+// embedding that starts them. All arithmetic is float32; only the normed output may be bfloat16.
+//
+// The streams of a token lie together: X [tokens, s, d] float32. A branch (a mixer or a feed-forward) with
+// connection (a [s], M [s, s], c [s]) and multiplier m reads u = sum_s a[s] X[s] and, once its output y is
+// there, the streams become X'[t] = sum_s M[s, t] X[s] + m c[t] y for every t at once. What runs between two
+// branches is one kernel here: it applies the write of the branch before (if any), stores the new streams,
+// reads for the branch after and norms what it read, out = w * u / sqrt(mean(u^2) + eps). With a = 1 and a
+// list of rows it is the model's end: the sum of the streams of the wanted rows, normed.
+// With one stream, a = M = c = 1, this is the residual sum with a multiplier, x += m y.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+
+#define STREAMS_MAX 8
+
+struct StreamsStep {
+    float *x;             // [tokens, s, d]
+    const float *y;       // [tokens, d] or null: no write pending
+    const float *mix;     // [s, s] indexed [from, to] (used with y)
+    const float *leave;   // [s] (used with y)
+    float mult;
+    const float *enter;   // [s]: the read
+    const float *w;       // [d] the norm's weight as it multiplies, or null: out = u, not normed
+    float eps;
+    void *out;            // [rows, d]
+    const int *rows;      // null: every row, and the new streams are stored; else output row r is made from row
+                          // rows[r] and x is left as it is
+    int s, d;
+};
+
+template <typename TO> __global__ void __launch_bounds__(256) streams_step_kernel(StreamsStep p) {
+    extern __shared__ float u_s[];  // [d]
+    __shared__ float scratch[33];
+    __shared__ float mix_s[STREAMS_MAX * STREAMS_MAX], leave_s[STREAMS_MAX], enter_s[STREAMS_MAX];
+    const int s = p.s, d = p.d;
+    // the connections are weights: they may be read ahead of the wait
+    if (threadIdx.x < s * s && p.y) mix_s[threadIdx.x] = p.mix[threadIdx.x];
+    if (threadIdx.x < s) {
+        leave_s[threadIdx.x] = p.y ? p.mult * p.leave[threadIdx.x] : 0.0f;
+        enter_s[threadIdx.x] = p.enter[threadIdx.x];
+    }
+    pdl_wait();
+    __syncthreads();
+    const int r = blockIdx.x;
+    const long long src = p.rows ? p.rows[r] : r;
+    float *xr = p.x + src * s * d;
+    const float *yr = p.y ? p.y + src * d : nullptr;
+    const bool store = yr && !p.rows;
+    float ss = 0.0f;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float old[STREAMS_MAX], now[STREAMS_MAX];
+#pragma unroll
+        for (int a = 0; a < STREAMS_MAX; a++)
+            if (a < s) old[a] = xr[(long long)a * d + j];
+        float u = 0.0f;
+        if (yr) {
+            const float yv = yr[j];
+#pragma unroll
+            for (int t = 0; t < STREAMS_MAX; t++) {
+                if (t < s) {
+                    float acc = 0.0f;
+#pragma unroll
+                    for (int a = 0; a < STREAMS_MAX; a++)
+                        if (a < s) acc = fmaf(mix_s[a * s + t], old[a], acc);
+                    now[t] = fmaf(leave_s[t], yv, acc);
+                    if (store) xr[(long long)t * d + j] = now[t];
+                }
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < STREAMS_MAX; t++)
+                if (t < s) now[t] = old[t];
+        }
+#pragma unroll
+        for (int t = 0; t < STREAMS_MAX; t++)
+            if (t < s) u = fmaf(enter_s[t], now[t], u);
+        u_s[j] = u;
+        ss += u * u;
+    }
+    TO *o = (TO *)p.out + (long long)r * d;
+    if (!p.w) {  // the read itself
+        for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_float<TO>(u_s[j]);
+        return;
+    }
+    ss = block_sum(ss, scratch);
+    const float scale = 1.0f / sqrtf(ss / (float)d + p.eps);
+    for (int j = threadIdx.x; j < d; j += blockDim.x) o[j] = from_float<TO>(p.w[j] * (u_s[j] * scale));
+}
+
+extern "C" int abk_streams_step(float *x, const float *y, const float *mix, const float *leave, float mult,
+                                const float *enter, const float *w, float eps, void *out, int out_dtype,
+                                const int *rows, int n_rows, int s, int d, void *stream) {
+    if (n_rows <= 0) return 0;
+    if (s < 1 || s > STREAMS_MAX) ABK_REFUSE("streams: %d streams, the kernel takes 1 to %d", s, STREAMS_MAX);
+    if (d < 1 || d > 12288) ABK_REFUSE("streams: width %d is more than a row in shared memory (12288)", d);
+    StreamsStep p;
+    p.x = x, p.y = y, p.mix = mix, p.leave = leave, p.mult = mult, p.enter = enter, p.w = w, p.eps = eps;
+    p.out = out, p.rows = rows, p.s = s, p.d = d;
+    const int threads = d >= 1024 ? 256 : 128;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (out_dtype == ABK_BF16)
+        abk_launch(streams_step_kernel<__nv_bfloat16>, dim3(n_rows), dim3(threads), (size_t)d * 4, st, p);
+    else
+        abk_launch(streams_step_kernel<float>, dim3(n_rows), dim3(threads), (size_t)d * 4, st, p);
+    return ABK_LAUNCH_RESULT();
+}
+
+// ------------------------------------------------------------------ embedding with a scale and a hashed pair table
+// x[t, a, :] = float(table[tok]) * scale + float(pairs[row]) for every stream a, where
+// row = (prev * mul_prev + tok * mul_cur) mod buckets and prev is the token before in the same sequence: the row
+// above in this step, or, for a sequence's first row of the step, the token its slot remembers. A sequence's first
+// token takes row `buckets`, the table's last. pairs null: no pair table.
+struct EmbedPairs {
+    const int *tokens, *token_seq, *token_pos, *seq_slot, *seq_pos0;
+    const void *table, *pairs;
+    const int *remembered;  // [slots]
+    float *x;
+    float scale;
+    int d, vocab, s;
+    long long buckets, mul_prev, mul_cur;
+    int *status;
+};
+
+template <typename TW> __global__ void embed_pairs_kernel(EmbedPairs p) {
+    pdl_wait();
+    const int t = blockIdx.x, d = p.d;
+    const int seq = p.token_seq[t];
+    float *out = p.x + (long long)t * p.s * d;
+    if (seq < 0) {  // padding
+        for (int j = threadIdx.x; j < p.s * d; j += blockDim.x) out[j] = 0.0f;
+        return;
+    }
+    const int tok = p.tokens[t], pos = p.token_pos[t];
+    bool bad = tok < 0 || tok >= p.vocab;
+    long long row = p.buckets;
+    if (p.pairs && pos > 0) {
+        int prev = pos > p.seq_pos0[seq] ? p.tokens[t - 1] : p.remembered[p.seq_slot[seq]];
+        if (prev < 0 || prev >= p.vocab) bad = true, prev = 0;
+        row = ((long long)prev * p.mul_prev + (long long)(bad ? 0 : tok) * p.mul_cur) % p.buckets;
+    }
+    if (bad && threadIdx.x == 0) atomicOr(p.status, 1);
+    const TW *e = (const TW *)p.table + (long long)(bad ? 0 : tok) * d;
+    const TW *b = p.pairs ? (const TW *)p.pairs + row * d : nullptr;
+    for (int j = threadIdx.x; j < d; j += blockDim.x) {
+        float v = bad ? 0.0f : to_float(e[j]) * p.scale;
+        if (b && !bad) v += to_float(b[j]);
+        for (int a = 0; a < p.s; a++) out[(long long)a * d + j] = v;
+    }
+}
+
+extern "C" int abk_embed_pairs(const int *tokens, const int *token_seq, const int *token_pos, const int *seq_slot,
+                               const int *seq_pos0, const void *table, const void *pairs, int table_dtype,
+                               const int *remembered, float *x, float scale, int n_tokens, int d, int vocab, int s,
+                               long long buckets, long long mul_prev, long long mul_cur, int *status, void *stream) {
+    if (n_tokens <= 0) return 0;
+    if (pairs && buckets < 1) ABK_REFUSE("embedding: a pair table of %lld buckets", buckets);
+    EmbedPairs p;
+    p.tokens = tokens, p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.seq_pos0 = seq_pos0;
+    p.table = table, p.pairs = pairs, p.remembered = remembered, p.x = x, p.scale = scale, p.d = d, p.vocab = vocab;
+    p.s = s, p.buckets = buckets, p.mul_prev = mul_prev, p.mul_cur = mul_cur, p.status = status;
+    const int threads = d >= 1024 ? 256 : 128;
+    cudaStream_t st = (cudaStream_t)stream;
+    if (table_dtype == ABK_BF16)
+        abk_launch(embed_pairs_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(threads), 0, st, p);
+    else
+        abk_launch(embed_pairs_kernel<float>, dim3(n_tokens), dim3(threads), 0, st, p);
+    return ABK_LAUNCH_RESULT();
+}
+
+// Every sequence of the step leaves its last token with its slot (a kernel of its own: the embedding above reads
+// what the step before left while other rows of the same sequence are still looked up).
+__global__ void remember_tokens_kernel(const int *tokens, const int *seq_start, const int *seq_slot, int n_seqs,
+                                       int *remembered) {
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n_seqs) return;
+    const int a = seq_start[i], b = seq_start[i + 1];
+    if (b > a) remembered[seq_slot[i]] = tokens[b - 1];
+}
+
+extern "C" int abk_remember_tokens(const int *tokens, const int *seq_start, const int *seq_slot, int n_seqs,
+                                   int *remembered, void *stream) {
+    if (n_seqs <= 0) return 0;
+    abk_launch(remember_tokens_kernel, dim3((n_seqs + 127) / 128), dim3(128), 0, (cudaStream_t)stream, tokens, seq_start,
+               seq_slot, n_seqs, remembered);
+    return ABK_LAUNCH_RESULT();
+}

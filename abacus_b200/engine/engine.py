@@ -16,6 +16,7 @@ from ..cache import SequenceCache
 from ..config.registry import load_config
 from ..models.model import Model
 from ..weights.loader import load_folder
+from ..weights.safetensors_io import folder_shapes
 from .batch import Sequence, StepBatch
 from .cstep import CStep
 from .graphs import DecodeGraphs, PromptGraphs
@@ -38,6 +39,8 @@ def load_model(folder, dtype="bfloat16", device=None):
     """A Model from a folder with config.json and *.safetensors; the class is chosen by config.json."""
     dtype = DTYPES[dtype] if isinstance(dtype, str) else dtype
     arch, config = load_config(folder)
+    if hasattr(arch, "complete_config"):  # sizes that config.json leaves to the tensors' shapes
+        config = arch.complete_config(config, folder_shapes(folder))
     spec = config.to_spec()
     layout = arch.layout(spec)
     tensors = load_folder(folder, lambda available: arch.tensor_names(spec, available))
@@ -66,7 +69,8 @@ class Engine:
         spec = model.spec
         context = min(max_context or spec.max_positions, spec.max_positions)
         self.cache = SequenceCache(model.cache_needs(), model.cache_sources(), max_tokens, model.ctx.dtype,
-                                   model.ctx.device, max_slots=max_slots, max_context=context)
+                                   model.ctx.device, max_slots=max_slots, max_context=context,
+                                   frame_need=model.frame_need())
         self.max_context = self.cache.max_context
         model.prepare(self.max_context)
         self.vocab = spec.vocab

@@ -48,13 +48,17 @@ class DecodeGraph:
     def capture(self, sequences):
         model = self.engine.model
         self.batch.fill(sequences, pad_logits=True)
-        # once outside a capture: loads the kernel libraries, sets function attributes, sizes the workspace
+        # once outside a capture: loads the kernel libraries, sets function attributes, sizes the workspace. That run
+        # is not the step: what it does to the sequences' recurrent states is taken back (the step itself is the
+        # first replay)
+        saved = self.engine.cache.save_states([s.slot for s in sequences])
         side = torch.cuda.Stream(device=model.ctx.device)
         side.wait_stream(torch.cuda.current_stream())
         with torch.cuda.stream(side):
             self.engine.forward(self.batch)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
+        self.engine.cache.restore_states(saved)
         from ..kernels import ops
         before = ops.LAUNCHES
         self.graph = torch.cuda.CUDAGraph()

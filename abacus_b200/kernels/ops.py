@@ -114,7 +114,7 @@ def swiglu(gate_up, act, block=None):
 
 
 def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved,
-             cache, q_only=False):
+             cache, q_only=False, v_dim=None):
     """Per-head norm of q and k, rotary encoding, and the cache write of k and v (src/model.c:247-259).
 
     qkv [T, (Hq + 2 Hkv) * hd] is changed in place. batch: engine.batch.StepBatch. cache: a
@@ -123,13 +123,26 @@ def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos
     _need_cuda(qkv, q_norm, k_norm, cos, sin)
     lib = load_module("elementwise")
     n = batch.n_rows
-    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + 2 * n_kv_heads) * head_dim and qkv.shape[0] >= n
+    vd = v_dim or head_dim
+    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd and qkv.shape[0] >= n
     if cos is not None:
         assert cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rotary_dim // 2
         if batch.max_position >= cos.shape[0]:
             raise KernelError(f"position {batch.max_position} is beyond the rotary table of {cos.shape[0]} positions")
     if cache is not None:
         assert cache.k.dtype == qkv.dtype and cache.k.shape[1:] == (n_kv_heads, cache.tokens_per_page, head_dim)
+        assert cache.v.shape[1:] == (n_kv_heads, cache.tokens_per_page, vd)
+    pinned = cache.pinned_pages if cache is not None else 0
+    if vd != head_dim or pinned:  # the general kernel alone takes values of another size and pinned first pages
+        _check(lib, lib.abk_qkv_prep_general(
+            _p(qkv), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(1 if q_only else 0),
+            _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_len_after), _p(q_norm),
+            _p(k_norm), _f(eps or 0.0), _p(cos), _p(sin), _i(rotary_dim), _i(1 if interleaved else 0),
+            _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
+            _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
+            _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
+            _i(vd), _i(pinned), _stream()), "qkv_prep")
+        return
     _check(lib, lib.abk_qkv_prep(
         _p(qkv), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(1 if q_only else 0),
         _p(batch.token_seq),
@@ -148,30 +161,37 @@ def advance_decode(batch):
                                        _p(batch.seq_len_after), _i(batch.n_seqs), _stream()), "advance_decode")
 
 
-def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False):
+def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, v_dim=None,
+                      keep_first=0, sink=None, exact_weights=False):
     """Causal grouped-query attention of every token of the step (src/model.c:197-211).
 
     q is read from qkv's q columns. Keys and values come from `cache` (a cache.LayerView), or, with
     from_step, from this step's own rows of qkv (only right when every sequence starts at position 0).
+    v_dim: the size of a value head (default head_dim). keep_first (with a window): the sequence's first keys
+    stay visible. sink: float32 [n_heads], a score per head that joins the denominator. exact_weights: the
+    softmax's weights stay float32 in the second product.
     """
-    _need_cuda(qkv, out)
+    _need_cuda(qkv, out, sink)
     lib = load_module("attention_generic")
     n = batch.n_rows
-    row = (n_heads + 2 * n_kv_heads) * head_dim
+    vd = v_dim or head_dim
+    row = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
     assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.dtype == qkv.dtype
-    assert out.shape[1] == n_heads * head_dim and out.shape[0] >= n and qkv.shape[0] >= n
+    assert out.shape[1] == n_heads * vd and out.shape[0] >= n and qkv.shape[0] >= n
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads)
     esize = qkv.element_size()
     k_step = ctypes.c_void_p(qkv.data_ptr() + n_heads * head_dim * esize) if from_step else ctypes.c_void_p(0)
     v_step = ctypes.c_void_p(qkv.data_ptr() + (n_heads + n_kv_heads) * head_dim * esize) if from_step else ctypes.c_void_p(0)
     if not from_step:
-        assert cache is not None and cache.k.dtype == qkv.dtype
-    _check(lib, lib.abk_attention_generic(
+        assert cache is not None and cache.k.dtype == qkv.dtype and cache.v.shape[-1] == vd
+    _check(lib, lib.abk_attention_general(
         _p(qkv), _ll(row), _p(out), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _f(scale),
         _i(window or 0), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_start),
         _p(batch.seq_pos0), _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
         _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
         _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
-        k_step, v_step, _ll(row), _stream()), "attention")
+        k_step, v_step, _ll(row), _i(vd), _i(keep_first or 0), _i(cache.pinned_pages if cache is not None else 0),
+        _p(sink), _i(1 if exact_weights else 0), _stream()), "attention")
 
 
 def gemm_simt(x, w, out, m=None):
@@ -329,11 +349,18 @@ def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None)
 
 
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None,
-              prepare=None):
+              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one. lists: the step's tiles and work list for the prefill kernels
     (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel.
-    prepare: see attention_decode (only where attention_decode_prepares() said yes for this step)."""
+    prepare: see attention_decode (only where attention_decode_prepares() said yes for this step).
+    v_dim, keep_first, sink, exact_weights: see attention_generic and attention_window; the kernels for plain heads
+    take none of them."""
+    if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights:
+        assert prepare is None, "q, k and v must be prepared before these kernels"
+        attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step,
+                          v_dim=v_dim, keep_first=keep_first, sink=sink, exact_weights=exact_weights)
+        return
     if (batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
             and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)):
         attention_decode(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, prepare=prepare)
@@ -621,3 +648,110 @@ def gemm_tc(x, w, out, m=None, tile_n=0, swap=-1, splits=0, persistent=-1):
     _check(lib, lib.abk_gemm_tc(_p(x), _p(w), _p(out), _i(_dt(out)), _i(m), _i(n), _i(k), _ll(x.stride(0)),
                                 _ll(w.stride(0)), _ll(out.stride(0)), _p(sc.gemm_floats), _p(sc.gemm_tickets),
                                 _p(sc.status), _i(tile_n), _i(swap), _i(splits), _i(persistent), _stream()), "gemm_tc")
+
+
+# ------------------------------------------------------------------ streams (csrc/streams.cu)
+def streams_step(x, y, connection, mult, enter, weight, eps, out, rows=None, n_rows=None):
+    """What runs between two branches of a model whose residual stream is kept as several copies, x float32
+    [tokens, s, d]: the write of the branch before, X'[t] = sum_s mix[s, t] X[s] + mult * leave[t] * y (y float32
+    [tokens, d] or None: nothing pending; connection = (mix [s, s], leave [s])), stored in place; then the read for the
+    branch after, u = sum_s enter[s] X'[s], and its norm, out = weight * u / sqrt(mean(u^2) + eps) (weight None:
+    out = u). rows (int32): only those rows are made, into out[0:len(rows)], and x is left as it is."""
+    _need_cuda(x, y, enter, weight, out, rows)
+    lib = load_module("streams")
+    n_tokens, s, d = x.shape
+    n = n_rows if n_rows is not None else (rows.numel() if rows is not None else n_tokens)
+    mix, leave = connection if y is not None else (None, None)
+    assert x.dtype == torch.float32 and x.is_contiguous() and out.is_contiguous() and out.shape[-1] == d and out.shape[0] >= n
+    assert y is None or (y.dtype == torch.float32 and y.is_contiguous() and y.shape[-1] == d and y.shape[0] >= (n if rows is None else 0))
+    assert enter.dtype == torch.float32 and enter.numel() == s
+    assert y is None or (mix.dtype == torch.float32 and mix.shape == (s, s) and mix.is_contiguous() and leave.numel() == s)
+    assert weight is None or (weight.dtype == torch.float32 and weight.numel() == d)
+    _check(lib, lib.abk_streams_step(_p(x), _p(y), _p(mix), _p(leave), _f(mult), _p(enter), _p(weight), _f(eps), _p(out),
+                                     _i(_dt(out)), _p(rows), _i(n), _i(s), _i(d), _stream()), "streams_step")
+
+
+def embed_pairs(batch, table, pairs, remembered, x, scale, buckets, mul_prev, mul_cur, status):
+    """x[t, a] = table[token] * scale + pairs[(previous token * mul_prev + token * mul_cur) mod buckets] for every
+    stream a (x float32 [tokens, s, d]); a sequence's first token takes row `buckets`; the token before a step's first
+    row is the one its slot remembers (remembered int32 [slots]). pairs None: no second table."""
+    _need_cuda(table, pairs, remembered, x, status)
+    lib = load_module("streams")
+    n, s, d = batch.n_rows, x.shape[1], x.shape[2]
+    assert x.dtype == torch.float32 and x.is_contiguous() and x.shape[0] >= n and table.is_contiguous() and table.shape[1] == d
+    assert pairs is None or (pairs.dtype == table.dtype and pairs.is_contiguous() and pairs.shape == (buckets + 1, d))
+    assert pairs is None or remembered.dtype == torch.int32
+    _check(lib, lib.abk_embed_pairs(_p(batch.tokens), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot),
+                                    _p(batch.seq_pos0), _p(table), _p(pairs), _i(_dt(table)), _p(remembered), _p(x),
+                                    _f(scale), _i(n), _i(d), _i(table.shape[0]), _i(s), _ll(buckets), _ll(mul_prev),
+                                    _ll(mul_cur), _p(status), _stream()), "embed_pairs")
+
+
+def remember_tokens(batch, remembered):
+    """remembered[slot] = the last token each sequence of the step brought."""
+    _need_cuda(remembered)
+    lib = load_module("streams")
+    n_seqs = batch.seq_slot.numel()
+    assert batch.seq_start.numel() >= n_seqs + 1 and remembered.dtype == torch.int32
+    _check(lib, lib.abk_remember_tokens(_p(batch.tokens), _p(batch.seq_start), _p(batch.seq_slot), _i(n_seqs),
+                                        _p(remembered), _stream()), "remember_tokens")
+
+
+# ------------------------------------------------------------------ the delta-rule mixer (csrc/delta_rule.cu)
+def short_conv(x, channels, weight, tail, out, batch):
+    """out[t, c] = silu(sum_j weight[c, j] * x[position - (taps - 1 - j), c]) over the first `channels` columns of x
+    (rows of any pitch), per sequence: zeros before its start, the slot's tail (float32 [slots, taps - 1, channels])
+    before this step's rows."""
+    _need_cuda(x, weight, tail, out)
+    lib = load_module("delta_rule")
+    n, taps = batch.n_rows, weight.shape[1]
+    assert x.stride(1) == 1 and x.shape[1] >= channels and out.is_contiguous() and out.shape[1] == channels
+    assert out.dtype == x.dtype and weight.dtype == torch.float32 and weight.shape == (channels, taps) and weight.is_contiguous()
+    assert tail.dtype == torch.float32 and tail.shape[1:] == (max(taps - 1, 0), channels) and tail.is_contiguous()
+    _check(lib, lib.abk_short_conv(_p(x), _ll(x.stride(0)), _p(out), _i(_dt(x)), _p(weight), _p(tail), _p(batch.token_seq),
+                                   _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_pos0), _i(n), _i(channels),
+                                   _i(taps), _stream()), "short_conv")
+
+
+def short_conv_tail(x, channels, taps, tail, batch):
+    """The slots' tails after the step: each sequence's last taps - 1 inputs (from x's rows, and from the old tail
+    where the step brought fewer)."""
+    _need_cuda(x, tail)
+    lib = load_module("delta_rule")
+    n_seqs = batch.seq_slot.numel()
+    assert x.stride(1) == 1 and tail.dtype == torch.float32 and tail.is_contiguous()
+    _check(lib, lib.abk_short_conv_tail(_p(x), _ll(x.stride(0)), _i(_dt(x)), _p(tail), _p(batch.seq_start),
+                                        _p(batch.seq_slot), _p(batch.seq_pos0), _i(n_seqs), _i(channels), _i(taps),
+                                        _stream()), "short_conv_tail")
+
+
+def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim):
+    """The gated delta rule over every sequence of the step, token by token, from and into the slots' states (float32
+    [slots, heads, value, key]). qkv [tokens, 2 * kv_heads * key + heads * value]: q, k and v after their convolution;
+    decay_in float32 [tokens, heads * key] before bias and softplus; beta_in [tokens, >= heads] (rows of any pitch)
+    before the sigmoid; out float32 [tokens, heads * value], not yet normed."""
+    _need_cuda(qkv, decay_in, beta_in, a_log, dt_bias, state, out)
+    lib = load_module("delta_rule")
+    n_seqs = batch.seq_slot.numel()
+    assert qkv.is_contiguous() and qkv.shape[1] == 2 * n_kv_heads * key_dim + n_heads * value_dim
+    assert decay_in.dtype == torch.float32 and decay_in.is_contiguous() and decay_in.shape[1] == n_heads * key_dim
+    assert beta_in.dtype == qkv.dtype and beta_in.stride(1) == 1 and beta_in.shape[1] >= n_heads
+    assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and dt_bias.numel() == n_heads * key_dim
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, value_dim, key_dim)
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == n_heads * value_dim
+    _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _p(beta_in),
+                                   _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.seq_start),
+                                   _p(batch.seq_slot), _i(n_seqs), _i(n_heads), _i(n_kv_heads), _i(key_dim),
+                                   _i(value_dim), _stream()), "delta_scan")
+
+
+def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps):
+    """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * sigmoid(gate[t, h]); o and gate float32
+    [tokens, heads * value], weight float32 [value]."""
+    _need_cuda(o, gate, weight, out)
+    lib = load_module("delta_rule")
+    assert o.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
+    assert o.is_contiguous() and gate.is_contiguous() and out.is_contiguous() and weight.numel() == value_dim
+    assert o.shape[1] == gate.shape[1] == out.shape[1] == n_heads * value_dim
+    _check(lib, lib.abk_gated_head_norm(_p(o), _p(gate), _p(weight), _p(out), _i(_dt(out)), _i(n_tokens), _i(n_heads),
+                                        _i(value_dim), _f(eps), _stream()), "gated_head_norm")

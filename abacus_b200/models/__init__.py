@@ -1,4 +1,4 @@
-from . import qwen3  # noqa: F401  (registers Qwen3ForCausalLM)
+from . import qwen3, temetar  # noqa: F401  (register Qwen3ForCausalLM and Temetar)
 from .layout import ModelLayout
 from .model import Model, expected_tensors
 

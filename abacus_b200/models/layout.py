@@ -14,3 +14,7 @@ class ModelLayout:
     final_norm: str
     head: str
     layers: list = field(default_factory=list)
+    frame: dict = field(default_factory=dict)  # further slots of the frame (parts/frame.py) -> tensor names
+
+    def frame_names(self):
+        return {"embed": self.embed, "final_norm": self.final_norm, "head": self.head, **self.frame}

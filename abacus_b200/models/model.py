@@ -25,7 +25,7 @@ def expected_tensors(spec, layout, available=None, blocks=None, frame=None):
     blocks = blocks or build_blocks(spec)
     frame = frame or FRAMES.build(spec)
     tied = spec.tied_head or (available is not None and layout.head not in available)
-    names = {"embed": layout.embed, "final_norm": layout.final_norm, "head": layout.head}
+    names = layout.frame_names()
     expected = {names[slot]: tuple(shape) for slot, shape in frame.param_shapes(tied).items()}
     for block, layer_names in zip(blocks, layout.layers):
         for part_name, part in block.parts().items():
@@ -46,7 +46,7 @@ class Model:
                     optional=set())
         ctx = self.ctx
         self.tied = layout.head not in expected
-        names = {"embed": layout.embed, "final_norm": layout.final_norm, "head": layout.head}
+        names = layout.frame_names()
         self.frame.bind({slot: tensors[names[slot]] for slot in self.frame.param_shapes(self.tied)}, ctx)
         for block, layer_names in zip(self.blocks, layout.layers):
             params = {pn: {slot: tensors[layer_names[(pn, slot)]] for slot in part.param_shapes()}
@@ -69,6 +69,11 @@ class Model:
     # what the cache must hold, entry by entry
     def cache_needs(self):
         return [self.blocks[e.layer].mixer.cache_need() if e.source is None else None for e in self.schedule]
+
+    def frame_need(self):
+        """What the frame keeps per sequence (a CacheNeed with states), or None."""
+        need = getattr(self.frame, "cache_need", None)
+        return need() if need else None
 
     def cache_sources(self):
         return [e.source for e in self.schedule]
@@ -102,7 +107,10 @@ class Model:
     def forward(self, batch, cache):
         """Logits float32 [batch.n_logit_rows, vocab] of the wanted rows of this step."""
         ws = self.ws
-        x = self.frame.embed(batch, ws, self.status)
+        if self.frame_need() is not None:  # the frame has a state per sequence
+            x = self.frame.embed(batch, ws, self.status, cache.frame)
+        else:
+            x = self.frame.embed(batch, ws, self.status)
         y = None
         for i, entry in enumerate(self.schedule):
             y = self.blocks[entry.layer].forward(x, y, batch, cache.views[i], ws)

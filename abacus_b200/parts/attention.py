@@ -33,8 +33,16 @@ class Attention:
             raise ValueError(f"{s.n_heads} query heads do not divide into {s.n_kv_heads} kv heads")
         if s.head_dim % 8 or s.head_dim > 256:
             raise ValueError(f"head_dim {s.head_dim}: the attention kernels take multiples of 8 up to 256")
+        self.v_dim = s.v_head_dim or s.head_dim
+        if self.v_dim < 1 or self.v_dim > 256:
+            raise ValueError(f"v_head_dim {self.v_dim}: the attention kernels take value heads of up to 256")
+        if s.keep_first and s.window is None:
+            raise ValueError("keep_first goes with a window")
+        # what only the general kernel takes: values of another size, kept first keys, a sink, float32 weights
+        self.general = self.v_dim != s.head_dim or bool(s.keep_first) or s.sink or s.exact_weights
         self.position = POSITIONS.build(s.position) if s.position is not None else None
         self.q_size, self.kv_size = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
+        self.v_size = s.n_kv_heads * self.v_dim
         self.cos = self.sin = None
         # a step of several tokens of a windowed layer is checked on the host (it may have to be refused): such
         # steps cannot be replayed from a captured graph; single-token steps can
@@ -47,14 +55,16 @@ class Attention:
 
     def step_weights(self):
         """The tensors a step reads once whatever its size (for the bytes a decode step must move)."""
-        return [self.qkv_proj.weight, self.o_proj.weight, self.q_norm, self.k_norm]
+        return [self.qkv_proj.weight, self.o_proj.weight, self.q_norm, self.k_norm, self.sink]
 
     def param_shapes(self):
         s = self.spec
-        shapes = {"wq": (self.q_size, s.hidden), "wk": (self.kv_size, s.hidden), "wv": (self.kv_size, s.hidden),
-                  "wo": (s.hidden, self.q_size)}
+        shapes = {"wq": (self.q_size, s.hidden), "wk": (self.kv_size, s.hidden), "wv": (self.v_size, s.hidden),
+                  "wo": (s.hidden, s.n_heads * self.v_dim)}
         if s.qk_norm_eps is not None:
             shapes.update(q_norm=(s.head_dim,), k_norm=(s.head_dim,))
+        if s.sink:
+            shapes["sink"] = (s.n_heads,)
         return shapes
 
     def bind(self, params, ctx):
@@ -65,10 +75,12 @@ class Attention:
         self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
         self.q_norm = to_device(params["q_norm"], ctx, torch.float32) if "q_norm" in params else None
         self.k_norm = to_device(params["k_norm"], ctx, torch.float32) if "k_norm" in params else None
+        self.sink = to_device(params["sink"], ctx, torch.float32) if "sink" in params else None
 
     def cache_need(self):
         s = self.spec
-        return CacheNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window)
+        return CacheNeed(n_kv_heads=s.n_kv_heads, head_dim=s.head_dim, window=s.window, v_head_dim=self.v_dim,
+                         keep_first=s.keep_first if s.window is not None else 0)
 
     def prepare(self, max_positions, device):
         if self.position is not None:
@@ -77,8 +89,8 @@ class Attention:
     def forward(self, xn, out, batch, cache, ws):
         s = self.spec
         n = batch.n_rows
-        qkv = ws.get("qkv", (n, self.q_size + 2 * self.kv_size), self.ctx.dtype)
-        att = ws.get("att", (n, self.q_size), self.ctx.dtype)
+        qkv = ws.get("qkv", (n, self.q_size + self.kv_size + self.v_size), self.ctx.dtype)
+        att = ws.get("att", (n, s.n_heads * self.v_dim), self.ctx.dtype)
         writes = cache.owns_storage
         rotary_dim = self.position.rotary_dim if self.position else 0
         interleaved = self.position.interleaved if self.position else False
@@ -88,6 +100,7 @@ class Attention:
         w = self.qkv_proj.weight
         prepared = False  # by the product's own kernel: a prompt's heads in its epilogue
         if (PRODUCT_PREPARES and writes and not batch.is_decode and not from_step and w.dtype == torch.bfloat16
+                and not self.general
                 and ops.gemm_tc_qkv_takes(xn, w, qkv, n, s.n_heads, s.n_kv_heads, s.head_dim, cache.kv, self.q_norm,
                                           self.k_norm, self.cos, self.sin, rotary_dim, interleaved)):
             ops.gemm_tc_qkv(xn, w, qkv, s.n_heads, s.n_kv_heads, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
@@ -100,18 +113,20 @@ class Attention:
         prepare = None
         if prepared:
             pass
-        elif (DECODE_PREPARES and batch.is_decode and cache.kv is not None
+        elif (DECODE_PREPARES and batch.is_decode and cache.kv is not None and not self.general
                 and ops.attention_decode_prepares(qkv, s.n_heads, s.n_kv_heads, s.head_dim, cache.kv, self.q_norm,
                                                   self.k_norm, self.cos, self.sin, rotary_dim, interleaved)):
             prepare = dict(q_norm=self.q_norm, k_norm=self.k_norm, eps=s.qk_norm_eps, cos=self.cos, sin=self.sin, keep=writes)
         else:
             ops.qkv_prep(qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
-                         self.cos, self.sin, rotary_dim, interleaved, cache.kv if writes else None, q_only=not writes)
+                         self.cos, self.sin, rotary_dim, interleaved, cache.kv if writes else None, q_only=not writes,
+                         v_dim=self.v_dim)
         if from_step and (batch.any_continuation or not writes):
             raise ops.KernelRefused("windowed attention takes several tokens of a sequence only at its start, "
                                     "and only with keys of its own")
         mine = batch.plan.get(self.lists.name)
         ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
-                      from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare)
+                      from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare,
+                      v_dim=self.v_dim, keep_first=s.keep_first, sink=self.sink, exact_weights=s.exact_weights)
         self.o_proj.forward(att, out, n)
         return out

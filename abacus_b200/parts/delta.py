@@ -1,0 +1,112 @@
+"""A recurrent mixer: the gated delta rule with a decay per head and key channel (config.specs.DeltaRuleSpec).
+
+Per head a float32 state S [key, value], zero at a sequence's start and carried from token to token:
+    S <- diag(g) S;   e = b (v - S^T k);   S <- S + k e^T;   o = S^T q
+The mixer owns everything around it: one stacked product for q, k, v, the write strength b and the inner vectors of
+the decay and of the output gate; the short causal convolution and SiLU on q, k and v; the two small products that
+widen the inner vectors; the per-head norm of o with its gate; the output product. Its cache is a state per sequence
+and entry: S, and the last inputs of the convolution. It keeps no keys, so its cost per token does not grow.
+
+Everything that enters the recurrence is float32 (unit vectors, decays, b, the state); q, k, v and the inner vectors
+leave their products in the model's storage type.
+"""
+import torch
+
+from ..cache.need import CacheNeed
+from ..kernels import ops
+from .base import MIXERS, to_device
+from .linear import Linear
+
+
+def _up8(n):
+    return -(-n // 8) * 8
+
+
+@MIXERS.register("channel_delta")
+class ChannelDelta:
+    capturable = True  # its forward launches kernels only; nothing in it depends on the step's contents
+
+    def __init__(self, spec):
+        s = self.spec = spec
+        if s.n_heads % s.n_kv_heads:
+            raise ValueError(f"{s.n_heads} heads do not divide into {s.n_kv_heads} key heads")
+        if not 1 <= s.key_dim <= 256:
+            raise ValueError(f"key_dim {s.key_dim}: the recurrence keeps up to 256 key channels a head")
+        if not 1 <= s.conv_taps <= 8:
+            raise ValueError(f"conv_taps {s.conv_taps}: the convolution takes 1 to 8 taps")
+        self.qk_size, self.v_size = s.n_kv_heads * s.key_dim, s.n_heads * s.value_dim
+        self.channels = 2 * self.qk_size + self.v_size  # what passes the convolution: q, k, v as they lie in a row
+        # columns of the stacked product: q, k, v, then b, the decay's inner vector, the gate's; each of the last three
+        # starts at a multiple of 8 elements, so that every part of a row is 16-byte aligned
+        self.at_b = _up8(self.channels)
+        self.at_decay = self.at_b + _up8(s.n_heads)
+        self.at_gate = self.at_decay + _up8(s.decay_rank)
+        self.width = self.at_gate + _up8(s.gate_rank)
+
+    def param_shapes(self):
+        s = self.spec
+        return {"wq": (self.qk_size, s.hidden), "wk": (self.qk_size, s.hidden), "wv": (self.v_size, s.hidden),
+                "conv_q": (self.qk_size, s.conv_taps), "conv_k": (self.qk_size, s.conv_taps),
+                "conv_v": (self.v_size, s.conv_taps), "wb": (s.n_heads, s.hidden),
+                "decay_in": (s.decay_rank, s.hidden), "decay_out": (s.n_heads * s.key_dim, s.decay_rank),
+                "decay_log": (s.n_heads,), "decay_bias": (s.n_heads * s.key_dim,),
+                "gate_in": (s.gate_rank, s.hidden), "gate_out": (self.v_size, s.gate_rank),
+                "out_norm": (s.value_dim,), "wo": (s.hidden, self.v_size)}
+
+    def bind(self, params, ctx):
+        s, self.ctx = self.spec, ctx
+        stacked = torch.zeros((self.width, s.hidden), dtype=params["wq"].dtype)
+        stacked[:self.channels] = torch.cat([params["wq"], params["wk"], params["wv"]], dim=0)
+        stacked[self.at_b:self.at_b + s.n_heads] = params["wb"]
+        stacked[self.at_decay:self.at_decay + s.decay_rank] = params["decay_in"]
+        stacked[self.at_gate:self.at_gate + s.gate_rank] = params["gate_in"]
+        self.in_proj = Linear(to_device(stacked, ctx, ctx.dtype))
+
+        def widened(w, rank):  # [n, rank] with its columns padded to the stacked product's part
+            padded = torch.zeros((w.shape[0], _up8(rank)), dtype=w.dtype)
+            padded[:, :rank] = w
+            return Linear(to_device(padded, ctx, ctx.dtype))
+        self.decay_out = widened(params["decay_out"], s.decay_rank)
+        self.gate_out = widened(params["gate_out"], s.gate_rank)
+        self.conv = to_device(torch.cat([params["conv_q"], params["conv_k"], params["conv_v"]], dim=0), ctx, torch.float32)
+        self.decay_log = to_device(params["decay_log"], ctx, torch.float32)
+        self.decay_bias = to_device(params["decay_bias"], ctx, torch.float32)
+        self.out_norm = to_device(params["out_norm"], ctx, torch.float32)
+        self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
+
+    def step_weights(self):
+        return [self.in_proj.weight, self.decay_out.weight, self.gate_out.weight, self.conv, self.decay_log,
+                self.decay_bias, self.out_norm, self.o_proj.weight]
+
+    def cache_need(self):
+        s = self.spec
+        return CacheNeed(states=(("delta", (s.n_heads, s.value_dim, s.key_dim), "float32"),
+                                 ("conv_tail", (max(s.conv_taps - 1, 0), self.channels), "float32")))
+
+    def state_bytes(self):
+        """Bytes of state a sequence holds in one entry (what a decode step reads and writes for it)."""
+        s = self.spec
+        return 4 * (s.n_heads * s.value_dim * s.key_dim + max(s.conv_taps - 1, 0) * self.channels)
+
+    def forward(self, xn, out, batch, cache, ws):
+        s, n, dt = self.spec, batch.n_rows, self.ctx.dtype
+        if not cache.owns_storage:
+            raise ops.KernelRefused("a delta-rule entry keeps a state of its own; it cannot read another entry's")
+        state, tail = cache.states["delta"], cache.states["conv_tail"]
+        proj = ws.get("delta_proj", (n, self.width), dt)
+        self.in_proj.forward(xn, proj, n)
+        qkv = ws.get("delta_qkv", (n, self.channels), dt)
+        ops.short_conv(proj, self.channels, self.conv, tail, qkv, batch)
+        if s.conv_taps > 1:
+            ops.short_conv_tail(proj, self.channels, s.conv_taps, tail, batch)
+        decay = ws.get("delta_decay", (n, s.n_heads * s.key_dim), torch.float32)
+        self.decay_out.forward(proj[:, self.at_decay:self.at_gate], decay, n)
+        gate = ws.get("delta_gate", (n, self.v_size), torch.float32)
+        self.gate_out.forward(proj[:, self.at_gate:self.width], gate, n)
+        o = ws.get("delta_o", (n, self.v_size), torch.float32)
+        ops.delta_scan(qkv, decay, proj[:, self.at_b:self.at_decay], self.decay_log, self.decay_bias, state, o, batch,
+                       s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim)
+        normed = ws.get("delta_normed", (n, self.v_size), dt)
+        ops.gated_head_norm(o, gate, self.out_norm, normed, n, s.n_heads, s.value_dim, s.norm_eps)
+        self.o_proj.forward(normed, out, n)
+        return out

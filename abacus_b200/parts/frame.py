@@ -59,3 +59,61 @@ class PlainFrame:
             self.final_norm.forward(x, y, xn, rows=batch.logit_rows, n_rows=r)
             self.head.forward(xn, out, r)
         return out
+
+
+@FRAMES.register("scaled_pairs")
+class PairsFrame:
+    """x = table[token] * scale, plus (with buckets > 0) a row of a second table chosen by the pair (previous token,
+    token): row (previous * mul_prev + token * mul_cur) mod buckets, or row `buckets` for a sequence's first token. The
+    previous token of a step's first row is part of the sequence's state (an int32 per slot, cache.frame). The stream
+    starts as `streams` copies of x, [rows, streams, hidden] (parts/streams.py); at the end the copies are summed,
+    normed and multiplied with the output matrix on the wanted rows. config.specs.PairEmbeddingSpec has the constants."""
+    capturable = True  # launches kernels only
+
+    def __init__(self, spec):
+        self.hidden, self.vocab = spec.hidden, spec.vocab
+        self.options = spec.frame_spec
+        self.final_norm = NORMS.build(spec.final_norm)
+
+    def param_shapes(self, tied):
+        shapes = {"embed": (self.vocab, self.hidden), "final_norm": tuple(self.final_norm.param_shapes()["weight"])}
+        if self.options.buckets > 0:
+            shapes["pairs"] = (self.options.buckets + 1, self.hidden)
+        if not tied:
+            shapes["head"] = (self.vocab, self.hidden)
+        return shapes
+
+    def cache_need(self):
+        from ..cache.need import CacheNeed
+        return CacheNeed(states=(("last_token", (), "int32"),)) if self.options.buckets > 0 else None
+
+    def bind(self, params, ctx):
+        self.ctx = ctx
+        self.table = to_device(params["embed"], ctx, ctx.dtype)
+        self.pairs = to_device(params["pairs"], ctx, ctx.dtype) if "pairs" in params else None
+        self.tied = "head" not in params
+        self.head = Linear(self.table if self.tied else to_device(params["head"], ctx, ctx.dtype))
+        self.final_norm.bind({"weight": params["final_norm"]}, ctx)
+        self.ones = torch.ones(self.options.streams, dtype=torch.float32, device=ctx.device)
+
+    def step_weights(self):
+        return [self.head.weight, *self.final_norm.step_weights()]
+
+    def embed(self, batch, ws, status, cache=None):
+        o = self.options
+        x = ws.get("x_streams", (batch.n_rows, o.streams, self.hidden), torch.float32)
+        remembered = cache.states["last_token"] if self.pairs is not None else None
+        ops.embed_pairs(batch, self.table, self.pairs, remembered, x, o.scale, o.buckets, o.mul_prev, o.mul_cur, status)
+        if self.pairs is not None:
+            ops.remember_tokens(batch, remembered)
+        return x
+
+    def logits(self, x, pending, batch, ws):
+        from .streams import read_streams
+        r = batch.n_logit_rows
+        out = ws.get("logits", (max(r, 1), self.vocab), torch.float32)[:r]
+        if r:
+            xn = ws.get("xn_final", (r, self.hidden), self.ctx.dtype)
+            read_streams(x, pending, self.ones, self.final_norm, xn, rows=batch.logit_rows, n_rows=r)
+            self.head.forward(xn, out, r)
+        return out

@@ -18,6 +18,8 @@ class RMSNorm:
 
     def bind(self, params, ctx):
         self.weight = to_device(params["weight"], ctx, torch.float32)
+        if getattr(self.spec, "one_plus", False):  # stored around zero: the kernels multiply by 1 + w, made once in float32
+            self.weight = (self.weight + 1.0).contiguous()
 
     def step_weights(self):
         return [self.weight]

@@ -54,23 +54,27 @@ def normal_values(key, first, count, mean, amplitude):
     return (np.float32(mean) + np.float32(amplitude) * unit_normal(key, first, count)).astype(np.float32)
 
 
-def _moments(name, shape, std, norm_std, scales):
-    """(mean, amplitude) of a tensor: 1-D tensors are norm weights, the rest matrices; `scales` multiplies both."""
+def _moments(name, shape, std, norm_std, scales, rule=None):
+    """(mean, amplitude) of a tensor: 1-D tensors are norm weights, the rest matrices; `scales` multiplies both.
+    rule(name, shape, std, norm_std) -> (mean, amplitude) or None: an architecture's own say about a tensor."""
     mean, amplitude = (1.0, norm_std) if len(shape) == 1 else (0.0, std)
+    own = rule(name, shape, std, norm_std) if rule is not None else None
+    if own is not None:
+        mean, amplitude = own
     for key, factor in (scales or {}).items():
         if key in name:
             mean, amplitude = mean * factor, amplitude * factor
     return float(np.float32(mean)), float(np.float32(amplitude))
 
 
-def random_tensor(name, shape, seed, std=0.02, norm_std=0.0, scales=None, device=None, dtype=torch.bfloat16):
+def random_tensor(name, shape, seed, std=0.02, norm_std=0.0, scales=None, device=None, dtype=torch.bfloat16, rule=None):
     """One tensor by name: 1-D tensors are norm weights, the rest matrices.
 
     scales: optional {substring of a name: factor} applied to the distribution, for tests that want, say,
     sharper attention. device: None or "cpu" makes it on the host; a CUDA device fills it there with the
     kernel. Both give the same bits.
     """
-    mean, amplitude = _moments(name, shape, std, norm_std, scales)
+    mean, amplitude = _moments(name, shape, std, norm_std, scales, rule)
     key = tensor_key(seed, name)
     count = int(np.prod(shape)) if len(shape) else 1
     device = torch.device(device) if device is not None else torch.device("cpu")
@@ -86,8 +90,8 @@ def random_tensor(name, shape, seed, std=0.02, norm_std=0.0, scales=None, device
     return out.reshape(tuple(shape))
 
 
-def random_tensors(expected, seed, std=0.02, norm_std=0.0, scales=None, device=None):
-    return {name: random_tensor(name, tuple(shape), seed, std, norm_std, scales, device)
+def random_tensors(expected, seed, std=0.02, norm_std=0.0, scales=None, device=None, rule=None):
+    return {name: random_tensor(name, tuple(shape), seed, std, norm_std, scales, device, rule=rule)
             for name, shape in expected.items()}
 
 
@@ -99,5 +103,6 @@ def write_random_model(folder, config, seed, std=0.02, norm_std=0.0, scales=None
     os.makedirs(folder, exist_ok=True)
     with open(os.path.join(folder, "config.json"), "w") as f:
         json.dump(config.to_dict(), f, indent=1)
-    save_tensors(os.path.join(folder, "model.safetensors"), random_tensors(expected, seed, std, norm_std, scales))
+    save_tensors(os.path.join(folder, "model.safetensors"),
+                 random_tensors(expected, seed, std, norm_std, scales, rule=getattr(arch, "random_moments", None)))
     return folder

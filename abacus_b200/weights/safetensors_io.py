@@ -79,6 +79,11 @@ def folder_index(folder):
     return index
 
 
+def folder_shapes(folder):
+    """{name: shape} of every tensor in a folder's files (headers only)."""
+    return {name: tuple(entry[2]) for name, entry in folder_index(folder).items()}
+
+
 class FolderReader:
     """Hands out tensors of a folder by name; the files are mapped, not read whole."""
 
