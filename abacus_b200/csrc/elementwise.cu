@@ -212,6 +212,7 @@ struct QkvPrep {
     void *qkv;
     int n_heads, n_kv_heads, head_dim;
     int v_dim = 0;  // size of a value head where it is not head_dim (0: head_dim); the general kernel alone takes it
+    long long row_size = 0;  // elements between rows of qkv where a row has padding behind its heads (0: none)
     int q_only;  // only the q heads are prepared (keys and values come from elsewhere)
     const int *token_seq, *token_pos, *seq_slot, *seq_len_after;
     const float *q_norm, *k_norm;
@@ -240,7 +241,8 @@ template <typename T> __global__ void qkv_prep_kernel(QkvPrep p) {
     bool is_q = head < p.n_heads, is_k = !is_q && head < p.n_heads + p.n_kv_heads;
     int kv_head = is_q ? 0 : is_k ? head - p.n_heads : head - p.n_heads - p.n_kv_heads;
     // a row of qkv: the q heads and the k heads of head_dim, then the v heads of vd
-    const long long row_size = (long long)(p.n_heads + p.n_kv_heads) * hd + (long long)p.n_kv_heads * vd;
+    const long long row_size =
+        p.row_size > 0 ? p.row_size : (long long)(p.n_heads + p.n_kv_heads) * hd + (long long)p.n_kv_heads * vd;
     T *row = (T *)p.qkv + (long long)t * row_size +
              (is_q || is_k ? (long long)head * hd : (long long)(p.n_heads + p.n_kv_heads) * hd + (long long)kv_head * vd);
     float *b = buf[warp];
@@ -445,13 +447,13 @@ template <int HD> __global__ void __launch_bounds__(FAST_WARPS * 32) qkv_prep_pr
     }
 }
 
-// v_dim: the size of a value head (0: head_dim); pinned_pages: see PagedCache.
+// v_dim: the size of a value head (0: head_dim); pinned_pages: see PagedCache; row_size: elements between rows of qkv.
 extern "C" int abk_qkv_prep_general(void *qkv, int dtype, int n_tokens, int n_heads, int n_kv_heads, int head_dim,
                                     int q_only, const int *token_seq, const int *token_pos, const int *seq_slot,
                                     const int *seq_len_after, const float *q_norm, const float *k_norm, float eps,
                                     const float *cos, const float *sin, int rotary_dim, int interleaved, void *k_pool,
                                     void *v_pool, const int *page_table, int table_width, int ring_pages,
-                                    int tokens_per_page, int v_dim, int pinned_pages, void *stream) {
+                                    int tokens_per_page, int v_dim, int pinned_pages, long long row_size, void *stream) {
     if (n_tokens <= 0) return 0;
     if (head_dim > MAX_HEAD_DIM || head_dim < 2 || head_dim % 2)
         ABK_REFUSE("qkv_prep: head_dim %d is not an even number up to %d", head_dim, MAX_HEAD_DIM);
@@ -459,7 +461,7 @@ extern "C" int abk_qkv_prep_general(void *qkv, int dtype, int n_tokens, int n_he
         ABK_REFUSE("qkv_prep: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
     QkvPrep p;
     p.qkv = qkv, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads, p.head_dim = head_dim, p.q_only = q_only;
-    p.v_dim = v_dim;
+    p.v_dim = v_dim, p.row_size = row_size;
     p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.seq_len_after = seq_len_after;
     p.q_norm = q_norm, p.k_norm = k_norm, p.eps = eps, p.cos = cos, p.sin = sin;
     p.rotary_dim = rotary_dim, p.interleaved = interleaved, p.k_pool = k_pool, p.v_pool = v_pool;

@@ -114,7 +114,7 @@ def swiglu(gate_up, act, block=None):
 
 
 def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos, sin, rotary_dim, interleaved,
-             cache, q_only=False, v_dim=None):
+             cache, q_only=False, v_dim=None, row=None):
     """Per-head norm of q and k, rotary encoding, and the cache write of k and v (src/model.c:247-259).
 
     qkv [T, (Hq + 2 Hkv) * hd] is changed in place. batch: engine.batch.StepBatch. cache: a
@@ -124,7 +124,9 @@ def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos
     lib = load_module("elementwise")
     n = batch.n_rows
     vd = v_dim or head_dim
-    assert qkv.is_contiguous() and qkv.shape[1] == (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd and qkv.shape[0] >= n
+    heads_size = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
+    row = row or heads_size  # a row may have padding behind its heads
+    assert qkv.is_contiguous() and qkv.shape[1] == row >= heads_size and qkv.shape[0] >= n
     if cos is not None:
         assert cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rotary_dim // 2
         if batch.max_position >= cos.shape[0]:
@@ -133,7 +135,8 @@ def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos
         assert cache.k.dtype == qkv.dtype and cache.k.shape[1:] == (n_kv_heads, cache.tokens_per_page, head_dim)
         assert cache.v.shape[1:] == (n_kv_heads, cache.tokens_per_page, vd)
     pinned = cache.pinned_pages if cache is not None else 0
-    if vd != head_dim or pinned:  # the general kernel alone takes values of another size and pinned first pages
+    if vd != head_dim or pinned or row != heads_size:  # the general kernel alone takes values of another size,
+        # pinned first pages and padded rows
         _check(lib, lib.abk_qkv_prep_general(
             _p(qkv), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(1 if q_only else 0),
             _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_len_after), _p(q_norm),
@@ -141,7 +144,7 @@ def qkv_prep(qkv, n_heads, n_kv_heads, head_dim, batch, q_norm, k_norm, eps, cos
             _p(cache.k if cache is not None else None), _p(cache.v if cache is not None else None),
             _p(cache.page_table if cache is not None else None), _i(cache.table_width if cache is not None else 0),
             _i(cache.ring_pages if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
-            _i(vd), _i(pinned), _stream()), "qkv_prep")
+            _i(vd), _i(pinned), _ll(row), _stream()), "qkv_prep")
         return
     _check(lib, lib.abk_qkv_prep(
         _p(qkv), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(1 if q_only else 0),
@@ -162,21 +165,23 @@ def advance_decode(batch):
 
 
 def attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, v_dim=None,
-                      keep_first=0, sink=None, exact_weights=False):
+                      keep_first=0, sink=None, exact_weights=False, row=None):
     """Causal grouped-query attention of every token of the step (src/model.c:197-211).
 
     q is read from qkv's q columns. Keys and values come from `cache` (a cache.LayerView), or, with
     from_step, from this step's own rows of qkv (only right when every sequence starts at position 0).
     v_dim: the size of a value head (default head_dim). keep_first (with a window): the sequence's first keys
     stay visible. sink: float32 [n_heads], a score per head that joins the denominator. exact_weights: the
-    softmax's weights stay float32 in the second product.
+    softmax's weights stay float32 in the second product. row: elements between rows of qkv where a row has padding
+    behind its heads.
     """
     _need_cuda(qkv, out, sink)
     lib = load_module("attention_generic")
     n = batch.n_rows
     vd = v_dim or head_dim
-    row = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
-    assert qkv.is_contiguous() and qkv.shape[1] == row and out.is_contiguous() and out.dtype == qkv.dtype
+    heads_size = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
+    row = row or heads_size
+    assert qkv.is_contiguous() and qkv.shape[1] == row >= heads_size and out.is_contiguous() and out.dtype == qkv.dtype
     assert out.shape[1] == n_heads * vd and out.shape[0] >= n and qkv.shape[0] >= n
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads)
     esize = qkv.element_size()
@@ -349,17 +354,17 @@ def sample_all(logits, temperature, rng_state, out, n_rows=None, rng_index=None)
 
 
 def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=False, ws=None, lists=None,
-              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False):
+              prepare=None, v_dim=None, keep_first=0, sink=None, exact_weights=False, row=None):
     """Attention of a step: picks the kernel for the phase and sizes; every case the faster kernels
     do not take goes to the general one. lists: the step's tiles and work list for the prefill kernels
     (parts/attention_plan.py: AttentionLists); without them a step of several tokens runs on the general kernel.
     prepare: see attention_decode (only where attention_decode_prepares() said yes for this step).
     v_dim, keep_first, sink, exact_weights: see attention_generic and attention_window; the kernels for plain heads
     take none of them."""
-    if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights:
+    if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights or row:
         assert prepare is None, "q, k and v must be prepared before these kernels"
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step,
-                          v_dim=v_dim, keep_first=keep_first, sink=sink, exact_weights=exact_weights)
+                          v_dim=v_dim, keep_first=keep_first, sink=sink, exact_weights=exact_weights, row=row)
         return
     if (batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
             and attention_decode_takes(n_heads, n_kv_heads, head_dim, cache)):

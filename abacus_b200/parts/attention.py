@@ -43,6 +43,9 @@ class Attention:
         self.position = POSITIONS.build(s.position) if s.position is not None else None
         self.q_size, self.kv_size = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
         self.v_size = s.n_kv_heads * self.v_dim
+        # a row of q, k and v is padded to a multiple of 8 elements, so that every row starts 16-byte aligned whatever
+        # the values' size (nothing to pad where values are as large as keys: head_dim is a multiple of 8)
+        self.row = -(-(self.q_size + self.kv_size + self.v_size) // 8) * 8
         self.cos = self.sin = None
         # a step of several tokens of a windowed layer is checked on the host (it may have to be refused): such
         # steps cannot be replayed from a captured graph; single-token steps can
@@ -70,6 +73,8 @@ class Attention:
     def bind(self, params, ctx):
         self.ctx = ctx
         wqkv = torch.cat([params["wq"], params["wk"], params["wv"]], dim=0)
+        if self.row > wqkv.shape[0]:
+            wqkv = torch.cat([wqkv, torch.zeros((self.row - wqkv.shape[0], wqkv.shape[1]), dtype=wqkv.dtype)], dim=0)
         self.qkv_proj = Linear(to_device(wqkv, ctx, ctx.dtype))
         self.q_proj = Linear(self.qkv_proj.weight[:self.q_size])  # for entries that read another entry's cache
         self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
@@ -89,7 +94,7 @@ class Attention:
     def forward(self, xn, out, batch, cache, ws):
         s = self.spec
         n = batch.n_rows
-        qkv = ws.get("qkv", (n, self.q_size + self.kv_size + self.v_size), self.ctx.dtype)
+        qkv = ws.get("qkv", (n, self.row), self.ctx.dtype)
         att = ws.get("att", (n, s.n_heads * self.v_dim), self.ctx.dtype)
         writes = cache.owns_storage
         rotary_dim = self.position.rotary_dim if self.position else 0
@@ -120,13 +125,14 @@ class Attention:
         else:
             ops.qkv_prep(qkv, s.n_heads, s.n_kv_heads, s.head_dim, batch, self.q_norm, self.k_norm, s.qk_norm_eps,
                          self.cos, self.sin, rotary_dim, interleaved, cache.kv if writes else None, q_only=not writes,
-                         v_dim=self.v_dim)
+                         v_dim=self.v_dim, row=self.row if self.general else None)
         if from_step and (batch.any_continuation or not writes):
             raise ops.KernelRefused("windowed attention takes several tokens of a sequence only at its start, "
                                     "and only with keys of its own")
         mine = batch.plan.get(self.lists.name)
         ops.attention(qkv, att, s.n_heads, s.n_kv_heads, s.head_dim, s.scale, s.window, batch, cache.kv,
                       from_step=from_step, ws=ws, lists=AttentionLists(mine) if mine is not None else None, prepare=prepare,
-                      v_dim=self.v_dim, keep_first=s.keep_first, sink=self.sink, exact_weights=s.exact_weights)
+                      v_dim=self.v_dim, keep_first=s.keep_first, sink=self.sink, exact_weights=s.exact_weights,
+                      row=self.row if self.general else None)
         self.o_proj.forward(att, out, n)
         return out

@@ -144,9 +144,9 @@ def channel_delta(h, p, c, eps, real, rnd=None):
     T = h.shape[0]
     H, G, K, V = c["heads"], c["kv_heads"], c["dim"], c["vdim"]
     lin = lambda x, name: _keep(rnd, x @ p[name].T)
-    q = _keep(rnd, silu(_keep(rnd, short_convolution(lin(h, "q"), p["q.conv"])))).reshape(T, G, K)
-    k = _keep(rnd, silu(_keep(rnd, short_convolution(lin(h, "k"), p["k.conv"])))).reshape(T, G, K)
-    v = _keep(rnd, silu(_keep(rnd, short_convolution(lin(h, "v"), p["v.conv"])))).reshape(T, H, V)
+    q = _keep(rnd, silu(short_convolution(lin(h, "q"), p["q.conv"]))).reshape(T, G, K)
+    k = _keep(rnd, silu(short_convolution(lin(h, "k"), p["k.conv"]))).reshape(T, G, K)
+    v = _keep(rnd, silu(short_convolution(lin(h, "v"), p["v.conv"]))).reshape(T, H, V)
     q = unit_vectors(q) * real(K) ** real(-0.5)
     k = unit_vectors(k)
     rep = H // G
