@@ -363,6 +363,11 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     take none of them."""
     if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights or row:
         assert prepare is None, "q, k and v must be prepared before these kernels"
+        if (exact_weights and not batch.is_decode and not batch.any_continuation
+                and attention_window_takes(qkv, head_dim, v_dim or head_dim, n_heads, n_kv_heads, row)):
+            attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=v_dim,
+                             keep_first=keep_first, sink=sink, row=row)  # whole prompts: keys from the step's rows
+            return
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step,
                           v_dim=v_dim, keep_first=keep_first, sink=sink, exact_weights=exact_weights, row=row)
         return
@@ -376,6 +381,37 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
         attention_prefill(qkv, out, n_heads, n_kv_heads, head_dim, scale, batch, cache, lists)
     else:
         attention_generic(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, from_step=from_step)
+
+
+def attention_window_takes(qkv, head_dim, v_dim, n_heads, n_kv_heads, row=None):
+    """Whether the tensor-core kernel for prompts with windows, sinks and values of their own size takes these sizes:
+    bfloat16, heads and values multiples of 8 (values up to 128), every part of a row 16-byte aligned."""
+    row = row or (n_heads + n_kv_heads) * head_dim + n_kv_heads * v_dim
+    return (qkv.dtype == torch.bfloat16 and head_dim % 8 == 0 and 8 <= head_dim <= 256 and v_dim % 8 == 0
+            and 8 <= v_dim <= 128 and row % 8 == 0 and qkv.data_ptr() % 16 == 0)
+
+
+def attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=None, keep_first=0, sink=None,
+                     row=None):
+    """Causal attention of whole prompts (every sequence of the step from its first token) on the warp-level tensor
+    cores, keys and values from the step's own rows of qkv: an optional window that also keeps the first keep_first
+    keys, an optional sink (float32 [n_heads]), values of v_dim, softmax weights in float32 (csrc/attention_window.cu)."""
+    _need_cuda(qkv, out, sink)
+    lib = load_module("attention_window")
+    vd = v_dim or head_dim
+    heads_size = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
+    row = row or heads_size
+    n, n_seqs = batch.n_rows, batch.seq_slot.numel()
+    assert qkv.dtype == torch.bfloat16 and out.dtype == torch.bfloat16 and qkv.is_contiguous() and out.is_contiguous()
+    assert qkv.shape[1] == row >= heads_size and out.shape[1] == n_heads * vd and qkv.shape[0] >= n and out.shape[0] >= n
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads)
+    if batch.any_continuation:
+        raise KernelRefused("attention_window reads keys from the step's rows: every sequence must start at position 0")
+    max_tiles = (n + 63) // 64 + n_seqs
+    _check(lib, lib.abk_attention_window(_p(qkv), _ll(row), _p(out), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(vd),
+                                         _i(n_heads * head_dim), _i((n_heads + n_kv_heads) * head_dim), _f(scale),
+                                         _i(window or 0), _i(keep_first or 0), _p(sink), _p(batch.seq_start), _i(n_seqs),
+                                         _i(max_tiles), _stream()), "attention_window")
 
 
 PREFILL_ON_MMA = False  # True: head size 128 too runs on the warp-level kernel (for comparison)

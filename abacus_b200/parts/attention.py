@@ -49,7 +49,9 @@ class Attention:
         self.cos = self.sin = None
         # a step of several tokens of a windowed layer is checked on the host (it may have to be refused): such
         # steps cannot be replayed from a captured graph; single-token steps can
-        self.capturable_prompts = s.window is None
+        # (so is a step of a layer with the general options: whether it may read its keys from the step's rows is
+        # decided from the step's contents)
+        self.capturable_prompts = s.window is None and not self.general
         self.lists = AttentionStepPlan(s.n_heads)  # the prefill kernels' tiles and work list, made per step
 
     def step_plans(self):

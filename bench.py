@@ -409,6 +409,115 @@ def run_ours(args):
     return 0
 
 
+# ------------------------------------------------------------------ another design beside the Qwen3 shape
+# Temetar at layer sizes of real models, beside the Qwen3 shape of equal width, depth, heads, feed-forward and
+# vocabulary: every fourth layer a delta rule (16 or 32 heads of 128 x 128 state), the others attention with a
+# window of 1,024 keys that keeps the first 4, a sink, half of each head rotated; four residual streams; a pair table.
+DESIGN_SIZES = {
+    "s": dict(width=1024, ff=3072, layers=28, heads=16, kv_heads=8, dim=128, vocab=151936, rank=64, qwen="0.6b"),
+    "m": dict(width=2560, ff=9728, layers=36, heads=32, kv_heads=8, dim=128, vocab=151936, rank=128, qwen="4b"),
+}
+
+
+def build_temetar(size):
+    import torch
+    from abacus_b200.config import get_architecture
+    from abacus_b200.config.temetar import TemetarAttention, TemetarConfig, TemetarDelta, TemetarLayer
+    from abacus_b200.models import Model
+    from abacus_b200.weights import random_tensors
+    z = DESIGN_SIZES[size]
+    att = TemetarAttention(z["heads"], z["kv_heads"], z["dim"], z["dim"], z["dim"] ** -0.5, 1000000.0, z["dim"] // 2, 1024, 4)
+    delta = TemetarDelta(z["heads"], z["kv_heads"], z["dim"], z["dim"], 4, z["rank"], z["rank"])
+    layers = tuple(TemetarLayer("channel_delta", delta, z["ff"]) if i % 4 == 0 else TemetarLayer("attention", att, z["ff"])
+                   for i in range(z["layers"]))
+    config = TemetarConfig(vocab=z["vocab"], width=z["width"], layers=layers, eps=1e-6, residual_mult=0.7, streams=4,
+                           embedding_scale=1.0, bigram=(65521, 31, 17))
+    arch = get_architecture("Temetar")
+    spec = config.to_spec()
+    expected, _ = arch.tensor_names(spec, None)
+    device = torch.device("cuda", 0)
+    tensors = random_tensors(expected, seed=5, std=0.02, device=device, rule=arch.random_moments)
+    model = Model(spec, arch.layout(spec), tensors, torch.bfloat16, device)
+    del tensors
+    torch.cuda.empty_cache()
+    return model
+
+
+def state_and_cache_bytes(model, tokens_held, n_seqs):
+    """Bytes of keys, values and recurrent state a decode step moves for n_seqs sequences that hold tokens_held
+    tokens together: a window's keys at most, a state read and written."""
+    total = 0.0
+    for need in model.cache_needs():
+        if need is None:
+            continue
+        if need.n_kv_heads:
+            per_seq = tokens_held / n_seqs
+            if need.window is not None:
+                per_seq = min(per_seq, need.window + need.keep_first)
+            total += n_seqs * per_seq * need.n_kv_heads * (need.head_dim + (need.v_head_dim or need.head_dim)) * 2
+        for _, shape, _ in need.states:
+            count = 1
+            for n in shape:
+                count *= n
+            total += 2 * 4 * count * n_seqs
+    return total
+
+
+def run_design(args):
+    """--design temetar: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3 shape of equal size."""
+    import torch
+    from abacus_b200.kernels import build_all
+    build_all(verbose=False)
+    torch.cuda.set_device(0)
+    pk = peaks()
+    z = DESIGN_SIZES[args.size]
+    out = {"design": "Temetar", "size": args.size, "shape": {k: v for k, v in z.items() if k != "qwen"},
+           "batch": args.batch, "prompt_tokens": PROMPT, "steps": args.steps, "warmup": args.warmup, "peaks": pk}
+    for which in ("temetar", "qwen3"):
+        if which == "temetar":
+            model = build_temetar(args.size)
+        else:
+            model, _ = build_model(z["qwen"])
+        prompts = prompts_for(args.batch, model.spec.vocab, 10 + args.batch)
+        run = device_decode(model, prompts, args.steps, args.warmup, CONTEXT, which == "temetar")
+        bytes_step = model.weight_bytes_read_per_step() + state_and_cache_bytes(model, run["mean_tokens_held"], args.batch)
+        one = prompts_for(1, model.spec.vocab, 99)[0][:PREFILL_TOKENS]
+        pre_ms, _ = prefill(model, [one]) if which == "qwen3" else prefill_any(model, [one])
+        out[which] = {"decode_tok_s": round(run["tok_s"], 1), "decode_ms_per_step": round(run["ms_step"], 4),
+                      "decode_bytes_per_step": int(bytes_step),
+                      "decode_hbm_frac": round(bytes_step / (run["ms_step"] / 1e3) / 1e9 / pk["hbm_gbs"], 4),
+                      "gpu_launches": run["launches"], "prefill_tok_s": round(PREFILL_TOKENS / (pre_ms / 1e3), 1),
+                      "prefill_ms": round(pre_ms, 3), "clocks": run["clocks"]}
+        del model
+        torch.cuda.empty_cache()
+    print(json.dumps(out))
+    return 0
+
+
+def prefill_any(model, prompts, context=CONTEXT, repeats=3):
+    """prefill() for a model whose FLOPs this file does not count: (median ms, None)."""
+    import torch
+    from abacus_b200.engine import Engine
+    engine = Engine(model, max_tokens=len(prompts) * context, max_slots=len(prompts), max_context=context)
+    times = []
+    for i in range(repeats + 2):
+        slots = [engine.open() for _ in prompts]
+        start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        start.record()
+        engine.step([(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+        end.record()
+        torch.cuda.synchronize()
+        if i >= 2:
+            times.append(start.elapsed_time(end))
+        for s in slots:
+            engine.close(s)
+    engine.check_status()
+    del engine
+    torch.cuda.empty_cache()
+    return statistics.median(times), None
+
+
 def run_reference(args):
     """abacus itself: its C engine built from an unmodified copy of its sources under baseline/_ref and run
     through its own command line (--bench PP TG, src/main.c:65-82) on a model its own converter made from the
@@ -474,11 +583,16 @@ def main():
     ap.add_argument("--config", default="0.6b", choices=sorted(CONFIGS), help="whose workload the line reports")
     ap.add_argument("--skip-large", action="store_true", help="leave the 4b and 8b workloads out of `points`")
     ap.add_argument("--ragged", action="store_true", help="with --only prefill: the configuration's own prompts")
+    ap.add_argument("--design", default=None, choices=["temetar"],
+                    help="instead of the default workload: this design at --size beside the Qwen3 shape of equal size")
+    ap.add_argument("--size", default="s", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")
     args = ap.parse_args()
     if args.gpus != 1:
         print(f"bench.py: this library runs on one GPU; --gpus {args.gpus} is not built (no multi-GPU path)")
         return 2
     args.warmup = max(args.warmup, 3)
+    if args.design and args.impl == "ours":
+        return run_design(args)
     return run_reference(args) if args.impl == "reference" else run_ours(args)
 
 

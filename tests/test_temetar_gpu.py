@@ -238,6 +238,10 @@ def test_attention_with_sink_window_and_kept_first_keys_in_prompts_and_decoding(
         ops.attention_generic(qkv, out, H, G, D, scale, window, b, kv, from_step=True, v_dim=V, keep_first=keep, sink=dev(sink),
                               exact_weights=True)
         np.testing.assert_allclose(out.float().cpu().numpy(), want, err_msg=f"prompt, loud {loud}", **tol)
+        if dtype == torch.bfloat16:  # the same prompt on the tensor-core kernel
+            fast = torch.empty_like(out)
+            ops.attention_window(qkv, fast, H, G, D, scale, window, b, v_dim=V, keep_first=keep, sink=dev(sink))
+            np.testing.assert_allclose(fast.float().cpu().numpy(), want, err_msg=f"prompt on tensor cores, loud {loud}", **tol)
         cache.advance(slot, T)
         # the prompt left its last window and its first keys in the cache: decode the last rows again from there
         if loud and loud[0] >= T - 5:
@@ -264,6 +268,34 @@ def test_attention_with_sink_window_and_kept_first_keys_in_prompts_and_decoding(
                     np.testing.assert_allclose(one.float().cpu().numpy(), want[i:i + 1], err_msg=f"decoded row {i}, loud {loud}", **tol)
                 cache.advance(slot, 1)
             cache.close_slot(slot)
+
+
+@pytest.mark.parametrize("H,G,D,V,window,keep,with_sink", [(4, 2, 16, 24, 12, 3, True), (6, 2, 24, 40, 70, 0, True),
+                                                          (3, 3, 32, 32, None, 0, False), (2, 2, 128, 128, 100, 7, True),
+                                                          (1, 1, 256, 64, 5, 0, True), (2, 1, 40, 8, 64, 64, False),
+                                                          (2, 1, 64, 128, 200, 130, True)])
+def test_the_tensor_core_prompt_kernel_on_unequal_prompts(H, G, D, V, window, keep, with_sink):
+    """Several sequences of unequal lengths in one step (one token, just under, at and just over a tile of 64 rows),
+    every row against the plain formulas; head sizes that need padding to 16, windows shorter and longer than a tile."""
+    from abacus_b200.kernels import ops
+    lens, scale = [150, 1, 37, 64, 65, 300], 0.11
+    rows, wants, sink = [], [], None
+    for i, T in enumerate(lens):
+        q, k, v, sk, _, _ = _attention_case(T, H, G, D, V, window, keep, scale, seed=100 + i)
+        q, k, v = plain.bf16_round(q), plain.bf16_round(k), plain.bf16_round(v)
+        sink = sk if sink is None else sink
+        z = np.einsum("ihd,jhd->hij", q, np.repeat(k, H // G, axis=1)) * np.float32(scale)
+        w = plain.softmax_with_sink(z, sink if with_sink else np.full(H, -np.inf, dtype=np.float32), plain.visible(T, window or T, keep))
+        wants.append(np.einsum("hij,jhv->ihv", w, np.repeat(v, H // G, axis=1)).reshape(T, H * V))
+        rows.append(np.concatenate([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], axis=1))
+    b = batch_of([(i, [0] * T, 0) for i, T in enumerate(lens)])
+    qkv = dev(np.concatenate(rows), torch.bfloat16)
+    out = torch.empty((sum(lens), H * V), dtype=torch.bfloat16, device=DEV)
+    assert ops.attention_window_takes(qkv, D, V, H, G)
+    ops.attention_window(qkv, out, H, G, D, scale, window, b, v_dim=V, keep_first=keep, sink=dev(sink) if with_sink else None)
+    got, want = out.float().cpu().numpy(), np.concatenate(wants)
+    # float32 weights: what is left is the rounding of the stored result
+    np.testing.assert_allclose(got, want, rtol=2 ** -8, atol=1e-3)
 
 
 def test_a_large_sink_takes_the_weight_and_no_sink_is_plain_softmax():
