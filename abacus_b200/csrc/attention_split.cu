@@ -1,0 +1,231 @@
+// Decode attention (one new token per sequence) over the paged cache with the general options (a window that also
+// keeps the first keys, a sink, values of another size than keys, float32 softmax weights), split along the keys so
+// that a handful of rows fills the GPU: a CTA takes 128 of a row's visible keys for all query heads of one kv head
+// (each key and value row is read once for the group), and leaves, per head, the maximum, the sum and the
+// unnormalised weighted values of its keys; a second kernel folds a row's parts, the sink among them.
+//
+//   key j is seen from position i when j <= i and (window == 0 or i - j < window or j < keep_first)
+//   p_j = exp(z_j - M) / (exp(sink - M) + sum_j exp(z_j - M)),  z_j = scale * (q . k_j),  out = sum_j p_j v_j
+//
+// A row's visible keys are numbered: first the kept first keys the window no longer reaches, then the window's
+// (or all). Part t has numbers [128 t, 128 t + 128). All arithmetic is float32.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+
+#define AS_THREADS 128
+#define AS_MAX_GROUP 16
+#define AS_MAX_DIM 256
+
+struct AttnSplit {
+    const void *q;       // row t, head h at q + t * q_row + h * head_dim
+    long long q_row;
+    float *parts;        // [tokens, heads, n_parts, v_dim + 2]: weighted values, then maximum and sum
+    void *out;           // [tokens, heads * v_dim]
+    int n_heads, n_kv_heads, head_dim, v_dim;
+    float scale;
+    int window, keep_first;
+    const float *sink;
+    const int *token_seq, *token_pos, *seq_slot;
+    const void *k_pool, *v_pool;
+    PagedCache cache, v_cache;
+    int n_parts;
+};
+
+// (first key of the window, number of kept first keys before it, number of visible keys) of a token at pos
+__device__ __forceinline__ void visible_keys(const AttnSplit &p, int pos, int &lo, int &kept, int &total) {
+    lo = p.window > 0 && pos - p.window + 1 > 0 ? pos - p.window + 1 : 0;
+    kept = p.keep_first < lo ? p.keep_first : lo;
+    total = kept + pos - lo + 1;
+}
+
+template <typename T> __device__ __forceinline__ float dot_q(const float *q, const T *k, int hd);
+template <> __device__ __forceinline__ float dot_q<float>(const float *q, const float *k, int hd) {
+    float acc = 0.0f;
+    for (int i = 0; i < hd; i += 4) {
+        float4 v = *(const float4 *)(k + i);
+        acc = fmaf(q[i], v.x, acc), acc = fmaf(q[i + 1], v.y, acc), acc = fmaf(q[i + 2], v.z, acc), acc = fmaf(q[i + 3], v.w, acc);
+    }
+    return acc;
+}
+template <> __device__ __forceinline__ float dot_q<__nv_bfloat16>(const float *q, const __nv_bfloat16 *k, int hd) {
+    float acc = 0.0f;
+    for (int i = 0; i < hd; i += 8) {
+        uint4 raw = *(const uint4 *)(k + i);
+        const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            float2 f = __bfloat1622float2(h[u]);
+            acc = fmaf(q[i + 2 * u], f.x, acc), acc = fmaf(q[i + 2 * u + 1], f.y, acc);
+        }
+    }
+    return acc;
+}
+
+template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_split_kernel(AttnSplit p) {
+    extern __shared__ float as_smem[];
+    const int group = p.n_heads / p.n_kv_heads, hd = p.head_dim, vd = p.v_dim;
+    float *q_s = as_smem;                      // [group][hd]
+    float *p_s = q_s + group * hd;             // [group][128]
+    float *red = p_s + group * AS_THREADS;     // [4][group] maxima, then sums
+    __shared__ long long v_off[AS_THREADS];
+    const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();
+    const int seq = p.token_seq[t];
+    if (seq < 0) return;
+    const int pos = p.token_pos[t], slot = p.seq_slot[seq];
+    int lo, kept, total;
+    visible_keys(p, pos, lo, kept, total);
+    if (part * AS_THREADS >= total) return;  // the fold knows how many parts a row has
+    const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)kvh * group * hd;
+    for (int e = tid; e < group * hd; e += AS_THREADS) q_s[e] = to_float(q[e]);
+    __syncthreads();
+    const int number = part * AS_THREADS + tid;
+    const bool valid = number < total;
+    float sc[AS_MAX_GROUP];
+    if (valid) {
+        const int j = number < kept ? number : lo + number - kept;
+        const int page = cache_page(p.cache, slot, j);
+        v_off[tid] = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, vd);
+        const T *k = (const T *)p.k_pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
+#pragma unroll
+        for (int g = 0; g < AS_MAX_GROUP; g++)
+            if (g < group) sc[g] = dot_q<T>(q_s + g * hd, k, hd) * p.scale;
+    } else {
+#pragma unroll
+        for (int g = 0; g < AS_MAX_GROUP; g++) sc[g] = -INFINITY;
+    }
+    // per head: the part's maximum, the weights against it, their sum
+#pragma unroll
+    for (int g = 0; g < AS_MAX_GROUP; g++) {
+        if (g < group) {
+            const float m = warp_max(sc[g]);
+            if (lane == 0) red[warp * group + g] = m;
+        }
+    }
+    __syncthreads();
+    float top[AS_MAX_GROUP];
+#pragma unroll
+    for (int g = 0; g < AS_MAX_GROUP; g++) {
+        if (g < group) {
+            top[g] = fmaxf(fmaxf(red[g], red[group + g]), fmaxf(red[2 * group + g], red[3 * group + g]));
+            sc[g] = valid ? expf(sc[g] - top[g]) : 0.0f;
+            p_s[g * AS_THREADS + tid] = sc[g];
+        }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int g = 0; g < AS_MAX_GROUP; g++) {
+        if (g < group) {
+            const float s = warp_sum(sc[g]);
+            if (lane == 0) red[warp * group + g] = s;
+        }
+    }
+    __syncthreads();
+    // weighted values: a thread a value column (two for values beyond 128), every head of the group per value read
+    const int n_valid = total - part * AS_THREADS < AS_THREADS ? total - part * AS_THREADS : AS_THREADS;
+    float acc0[AS_MAX_GROUP], acc1[AS_MAX_GROUP];
+#pragma unroll
+    for (int g = 0; g < AS_MAX_GROUP; g++) acc0[g] = acc1[g] = 0.0f;
+    const T *v_base = (const T *)p.v_pool;
+    if (tid < vd) {
+        for (int jj = 0; jj < n_valid; jj++) {
+            const T *v = v_base + v_off[jj];
+            const float a = to_float(v[tid]), b = tid + AS_THREADS < vd ? to_float(v[tid + AS_THREADS]) : 0.0f;
+#pragma unroll
+            for (int g = 0; g < AS_MAX_GROUP; g++) {
+                if (g < group) {
+                    const float w = p_s[g * AS_THREADS + jj];
+                    acc0[g] = fmaf(w, a, acc0[g]), acc1[g] = fmaf(w, b, acc1[g]);
+                }
+            }
+        }
+    }
+#pragma unroll
+    for (int g = 0; g < AS_MAX_GROUP; g++) {
+        if (g < group) {
+            float *dst = p.parts + (((long long)t * p.n_heads + kvh * group + g) * p.n_parts + part) * (vd + 2);
+            if (tid < vd) dst[tid] = acc0[g];
+            if (tid + AS_THREADS < vd) dst[tid + AS_THREADS] = acc1[g];
+            if (tid == 0) {
+                dst[vd] = top[g];
+                dst[vd + 1] = (red[g] + red[group + g]) + (red[2 * group + g] + red[3 * group + g]);
+            }
+        }
+    }
+}
+
+// out[t, h] = sum over the row's parts (and the sink) of their weighted values, over the sum of their sums, all
+// against the largest maximum. One CTA per (token, head), parts in order.
+template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_fold_kernel(AttnSplit p) {
+    const int t = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, vd = p.v_dim;
+    const float sink = p.sink ? p.sink[h] : -INFINITY;  // a weight: ahead of the wait
+    pdl_wait();
+    T *out = (T *)p.out + ((long long)t * p.n_heads + h) * vd;
+    const int seq = p.token_seq[t];
+    if (seq < 0) {
+        for (int d = tid; d < vd; d += AS_THREADS) out[d] = from_float<T>(0.0f);
+        return;
+    }
+    int lo, kept, total;
+    visible_keys(p, p.token_pos[t], lo, kept, total);
+    const int n = (total + AS_THREADS - 1) / AS_THREADS;
+    const float *src = p.parts + ((long long)t * p.n_heads + h) * p.n_parts * (vd + 2);
+    float top = sink;
+    for (int i = 0; i < n; i++) top = fmaxf(top, src[(long long)i * (vd + 2) + vd]);
+    float l = p.sink ? expf(sink - top) : 0.0f, a = 0.0f, b = 0.0f;
+    for (int i = 0; i < n; i++) {
+        const float *part = src + (long long)i * (vd + 2);
+        const float w = expf(part[vd] - top);
+        l = fmaf(part[vd + 1], w, l);
+        if (tid < vd) a = fmaf(part[tid], w, a);
+        if (tid + AS_THREADS < vd) b = fmaf(part[tid + AS_THREADS], w, b);
+    }
+    if (tid < vd) out[tid] = from_float<T>(a / l);
+    if (tid + AS_THREADS < vd) out[tid + AS_THREADS] = from_float<T>(b / l);
+}
+
+// max_keys: an upper bound of the keys any row of the step sees (its position + 1, or window + keep_first);
+// parts: float32 scratch of at least tokens * heads * ceil(max_keys / 128) * (v_dim + 2).
+extern "C" int abk_attention_split(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+                                   int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
+                                   const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
+                                   const void *k_pool, const void *v_pool, const int *page_table, int table_width,
+                                   int ring_pages, int pinned_pages, int tokens_per_page, int max_keys, float *parts,
+                                   long long parts_floats, void *stream) {
+    if (n_tokens <= 0) return 0;
+    if (head_dim > AS_MAX_DIM || head_dim % 8 || head_dim < 8) ABK_REFUSE("attention_split: head_dim %d is not a multiple of 8 up to %d", head_dim, AS_MAX_DIM);
+    if (v_dim < 1 || v_dim > AS_MAX_DIM) ABK_REFUSE("attention_split: value size %d is not 1 to %d", v_dim, AS_MAX_DIM);
+    if (n_kv_heads < 1 || n_heads % n_kv_heads || n_heads / n_kv_heads > AS_MAX_GROUP)
+        ABK_REFUSE("attention_split: %d query heads to %d kv heads (groups of up to %d)", n_heads, n_kv_heads, AS_MAX_GROUP);
+    if (n_heads > 65535 || max_keys < 1) ABK_REFUSE("attention_split: %d heads, %d keys", n_heads, max_keys);
+    AttnSplit p;
+    p.q = q, p.q_row = q_row, p.parts = parts, p.out = out, p.n_heads = n_heads, p.n_kv_heads = n_kv_heads;
+    p.head_dim = head_dim, p.v_dim = v_dim, p.scale = scale, p.window = window > 0 ? window : 0;
+    p.keep_first = window > 0 && keep_first > 0 ? keep_first : 0, p.sink = sink;
+    p.token_seq = token_seq, p.token_pos = token_pos, p.seq_slot = seq_slot, p.k_pool = k_pool, p.v_pool = v_pool;
+    p.cache.page_table = page_table, p.cache.table_width = table_width, p.cache.ring_pages = ring_pages;
+    p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
+    p.v_cache = p.cache;
+    p.n_parts = (max_keys + AS_THREADS - 1) / AS_THREADS;
+    if (p.n_parts > 65535) ABK_REFUSE("attention_split: %d keys are more than a grid takes", max_keys);
+    if ((long long)n_tokens * n_heads * p.n_parts * (v_dim + 2) > parts_floats)
+        ABK_REFUSE("attention_split: the scratch memory holds %lld floats, the step needs %lld", parts_floats,
+                   (long long)n_tokens * n_heads * p.n_parts * (v_dim + 2));
+    const int group = n_heads / n_kv_heads;
+    const size_t smem = (size_t)(group * head_dim + group * AS_THREADS + 4 * group) * 4;
+    cudaStream_t s = (cudaStream_t)stream;
+    const bool bf = dtype == ABK_BF16;
+    if (smem > 48 * 1024) {
+        cudaError_t e = abk_allow_shared_memory(bf ? (const void *)attention_split_kernel<__nv_bfloat16>
+                                                   : (const void *)attention_split_kernel<float>, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    dim3 grid(n_tokens, n_kv_heads, p.n_parts), fold(n_tokens, n_heads);
+    if (bf) abk_launch(attention_split_kernel<__nv_bfloat16>, grid, dim3(AS_THREADS), smem, s, p);
+    else abk_launch(attention_split_kernel<float>, grid, dim3(AS_THREADS), smem, s, p);
+    int rc = ABK_LAUNCH_RESULT();
+    if (rc) return rc;
+    if (bf) abk_launch(attention_fold_kernel<__nv_bfloat16>, fold, dim3(AS_THREADS), 0, s, p);
+    else abk_launch(attention_fold_kernel<float>, fold, dim3(AS_THREADS), 0, s, p);
+    return ABK_LAUNCH_RESULT();
+}

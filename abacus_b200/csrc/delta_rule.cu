@@ -9,9 +9,7 @@
 //
 // A value column of S never meets another: column j needs S[:, j], v_j and the token's q, k, g, b. So a thread
 // keeps (a part of) one column in registers and walks the sequence's tokens in order, and a prompt of any length
-// and a decode step are the same kernel. The key channels of a column are dealt to 1, 2, 4 or 8 neighbouring
-// lanes, 32 channels each, which meet by shuffles. The state is stored [head, value, key], so a lane's part is
-// one contiguous run.
+// and a decode step are the same kernel. The state is stored [head, value, key], so a column is one contiguous run.
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
 
@@ -56,6 +54,80 @@ template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(S
     *out = from_float<T>(acc / (1.0f + expf(-acc)));
 }
 
+// The same with VEC channels a thread (16 bytes of the storage type), for channel counts and row pitches that are
+// multiples of VEC with everything 16-byte aligned; a block has CONV_TOKENS tokens, its weights read once.
+#define CONV_TOKENS 4
+template <typename T, int VEC> struct ConvVector;
+template <> struct ConvVector<__nv_bfloat16, 8> {
+    static __device__ __forceinline__ void load(const __nv_bfloat16 *p, float *v) {
+        const uint4 raw = *(const uint4 *)p;
+        const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
+#pragma unroll
+        for (int u = 0; u < 4; u++) {
+            const float2 f = __bfloat1622float2(h[u]);
+            v[2 * u] = f.x, v[2 * u + 1] = f.y;
+        }
+    }
+    static __device__ __forceinline__ void store(__nv_bfloat16 *p, const float *v) {
+        uint4 raw;
+        __nv_bfloat162 *h = (__nv_bfloat162 *)&raw;
+#pragma unroll
+        for (int u = 0; u < 4; u++) h[u] = __floats2bfloat162_rn(v[2 * u], v[2 * u + 1]);
+        *(uint4 *)p = raw;
+    }
+};
+template <> struct ConvVector<float, 4> {
+    static __device__ __forceinline__ void load(const float *p, float *v) {
+        const float4 f = *(const float4 *)p;
+        v[0] = f.x, v[1] = f.y, v[2] = f.z, v[3] = f.w;
+    }
+    static __device__ __forceinline__ void store(float *p, const float *v) { *(float4 *)p = make_float4(v[0], v[1], v[2], v[3]); }
+};
+
+template <typename T, int VEC> __global__ void __launch_bounds__(128) short_conv_vec_kernel(ShortConv p) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC, taps = p.taps;
+    float w[VEC][CONV_MAX_TAPS];
+    if (c < p.channels) {
+#pragma unroll
+        for (int u = 0; u < VEC; u++)
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; j++) w[u][j] = j < taps ? p.w[(long long)(c + u) * taps + j] : 0.0f;  // weights: ahead of the wait
+    }
+    pdl_wait();
+    if (c >= p.channels) return;
+    for (int t = blockIdx.x * CONV_TOKENS; t < min(p.n_tokens, (blockIdx.x + 1) * CONV_TOKENS); t++) {
+        T *out = (T *)p.out + (long long)t * p.channels + c;
+        const int seq = p.token_seq[t];
+        float acc[VEC];
+#pragma unroll
+        for (int u = 0; u < VEC; u++) acc[u] = 0.0f;
+        if (seq >= 0) {
+            const int pos = p.token_pos[t], pos0 = p.seq_pos0[seq];
+            const float *tail = p.tail + (long long)p.seq_slot[seq] * (taps - 1) * p.channels + c;
+#pragma unroll
+            for (int j = 0; j < CONV_MAX_TAPS; j++) {
+                if (j < taps) {
+                    const int back = taps - 1 - j, at = pos - back;
+                    float v[VEC];
+                    if (at >= pos0) ConvVector<T, VEC>::load((const T *)p.in + (long long)(t - back) * p.ld + c, v);
+                    else if (at >= 0) {
+#pragma unroll
+                        for (int u = 0; u < VEC; u++) v[u] = tail[(long long)(at - (pos0 - (taps - 1))) * p.channels + u];
+                    } else {
+#pragma unroll
+                        for (int u = 0; u < VEC; u++) v[u] = 0.0f;
+                    }
+#pragma unroll
+                    for (int u = 0; u < VEC; u++) acc[u] = fmaf(w[u][j], v[u], acc[u]);
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < VEC; u++) acc[u] = acc[u] / (1.0f + expf(-acc[u]));
+        }
+        ConvVector<T, VEC>::store(out, acc);
+    }
+}
+
 extern "C" int abk_short_conv(const void *in, long long ld, void *out, int dtype, const float *w, const float *tail,
                               const int *token_seq, const int *token_pos, const int *seq_slot, const int *seq_pos0,
                               int n_tokens, int channels, int taps, void *stream) {
@@ -67,6 +139,13 @@ extern "C" int abk_short_conv(const void *in, long long ld, void *out, int dtype
     dim3 grid(n_tokens, (channels + 127) / 128);
     if (grid.y > 65535) ABK_REFUSE("short convolution: %d channels are more than a grid takes", channels);
     cudaStream_t s = (cudaStream_t)stream;
+    const int vec = dtype == ABK_BF16 ? 8 : 4;
+    if (channels % vec == 0 && ld % vec == 0 && !(((uintptr_t)in | (uintptr_t)out) & 15)) {
+        dim3 tiles((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels / vec + 127) / 128);
+        if (dtype == ABK_BF16) abk_launch(short_conv_vec_kernel<__nv_bfloat16, 8>, tiles, dim3(128), 0, s, p);
+        else abk_launch(short_conv_vec_kernel<float, 4>, tiles, dim3(128), 0, s, p);
+        return ABK_LAUNCH_RESULT();
+    }
     if (dtype == ABK_BF16) abk_launch(short_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, p);
     else abk_launch(short_conv_kernel<float>, grid, dim3(128), 0, s, p);
     return ABK_LAUNCH_RESULT();
@@ -110,7 +189,12 @@ extern "C" int abk_short_conv_tail(const void *in, long long ld, int dtype, floa
 }
 
 // ------------------------------------------------------------------ the recurrence
-#define SCAN_ROWS 32    // key channels a lane keeps
+// A thread keeps KR key channels of one value column in registers (KR = 32, 64 or 128: all of a column where the
+// key size allows, else the column's channels are dealt to 2, 4 or 8 neighbouring lanes that meet by shuffles), so
+// the lanes of a warp are different columns and read a token's q, k and g from shared memory at one address (a
+// broadcast). A block has 128 / lanes-per-column columns of one (sequence, head); a chunk of 16 tokens is prepared
+// together (unit vectors, decays, write strengths: a warp a token), then walked in order. The state comes in and
+// goes out through shared memory, so that global memory is read and written in whole lines.
 #define SCAN_CHUNK 16   // tokens prepared together
 #define SCAN_THREADS 128
 
@@ -126,22 +210,24 @@ struct DeltaScan {
     float *out;             // [tokens, heads * value]
     const int *seq_start, *seq_slot;
     int heads, kv_heads, key, value;
-    int parts;              // lanes to a column: 1, 2, 4 or 8; parts * SCAN_ROWS >= key
+    int parts;              // lanes to a column: 1, 2, 4 or 8; parts * KR >= key
     float q_scale;          // key^-1/2
 };
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
-template <typename T> __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaScan p) {
+template <typename T, int KR> __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaScan p) {
     extern __shared__ float smem[];
-    const int parts = p.parts, kp = parts * SCAN_ROWS;  // padded key size
+    const int parts = p.parts, kp = parts * KR;         // padded key size
     const int cols = SCAN_THREADS / parts;              // columns of this block
     float *k_s = smem;                                  // [chunk][kp]
     float *q_s = k_s + SCAN_CHUNK * kp;
     float *g_s = q_s + SCAN_CHUNK * kp;
     float *v_s = g_s + SCAN_CHUNK * kp;                 // [chunk][cols]
     float *b_s = v_s + SCAN_CHUNK * cols;               // [chunk]
+    float *stage = b_s + SCAN_CHUNK;                    // [warps][32 * 33]: 32 floats of each lane, a line at a time
     const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
+    const int warp = tid >> 5, lane = tid & 31, n_warps = SCAN_THREADS / 32;
     const int col = blockIdx.z * cols + tid / parts, part = tid % parts;
     const int K = p.key, V = p.value;
     const int kvh = h / (p.heads / p.kv_heads);
@@ -150,12 +236,23 @@ template <typename T> __global__ void __launch_bounds__(SCAN_THREADS) delta_scan
     const int row0 = p.seq_start[seq], n = p.seq_start[seq + 1] - row0;
     if (n <= 0) return;
     const bool live = col < V;
-    float *mine = p.state + (((long long)p.seq_slot[seq] * p.heads + h) * V + (live ? col : 0)) * K + part * SCAN_ROWS;
-    float S[SCAN_ROWS];
+    float *head_state = p.state + ((long long)p.seq_slot[seq] * p.heads + h) * V * K;
+    float *mine_stage = stage + warp * 32 * 33;
+    // lane j of this warp owns channels [part_j * KR, + KR) of column col_j
+    const int warp_col0 = blockIdx.z * cols + (warp * 32) / parts;
+    float S[KR];
 #pragma unroll
-    for (int i = 0; i < SCAN_ROWS; i++) S[i] = live && part * SCAN_ROWS + i < K ? mine[i] : 0.0f;
+    for (int c = 0; c < KR / 32; c++) {
+        for (int j = 0; j < 32; j++) {
+            const int cj = warp_col0 + j / parts, ch = (j % parts) * KR + c * 32 + lane;
+            mine_stage[j * 33 + lane] = cj < V && ch < K ? head_state[(long long)cj * K + ch] : 0.0f;
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < 32; i++) S[c * 32 + i] = mine_stage[lane * 33 + i];
+        __syncwarp();
+    }
 
-    const int warp = tid >> 5, lane = tid & 31, n_warps = SCAN_THREADS / 32;
     for (int base = 0; base < n; base += SCAN_CHUNK) {
         const int count = n - base < SCAN_CHUNK ? n - base : SCAN_CHUNK;
         __syncthreads();  // the chunk before is done with
@@ -189,37 +286,61 @@ template <typename T> __global__ void __launch_bounds__(SCAN_THREADS) delta_scan
         }
         __syncthreads();
         for (int c = 0; c < count; c++) {
-            const float4 *k4 = (const float4 *)(k_s + c * kp + part * SCAN_ROWS);
-            const float4 *q4 = (const float4 *)(q_s + c * kp + part * SCAN_ROWS);
-            const float4 *g4 = (const float4 *)(g_s + c * kp + part * SCAN_ROWS);
-            float seen = 0.0f;
+            const float4 *k4 = (const float4 *)(k_s + c * kp + part * KR);
+            const float4 *q4 = (const float4 *)(q_s + c * kp + part * KR);
+            const float4 *g4 = (const float4 *)(g_s + c * kp + part * KR);
+            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < SCAN_ROWS / 4; i++) {
+            for (int i = 0; i < KR / 4; i++) {
                 const float4 g = g4[i], k = k4[i];
                 S[4 * i] *= g.x, S[4 * i + 1] *= g.y, S[4 * i + 2] *= g.z, S[4 * i + 3] *= g.w;
-                seen = fmaf(S[4 * i], k.x, seen), seen = fmaf(S[4 * i + 1], k.y, seen);
-                seen = fmaf(S[4 * i + 2], k.z, seen), seen = fmaf(S[4 * i + 3], k.w, seen);
+                s0 = fmaf(S[4 * i], k.x, s0), s1 = fmaf(S[4 * i + 1], k.y, s1);
+                s2 = fmaf(S[4 * i + 2], k.z, s2), s3 = fmaf(S[4 * i + 3], k.w, s3);
             }
+            float seen = (s0 + s1) + (s2 + s3);
             for (int o = 1; o < parts; o <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
             const float e = b_s[c] * (v_s[c * cols + tid / parts] - seen);
-            float read = 0.0f;
+            s0 = s1 = s2 = s3 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < SCAN_ROWS / 4; i++) {
+            for (int i = 0; i < KR / 4; i++) {
                 const float4 k = k4[i], q = q4[i];
                 S[4 * i] = fmaf(k.x, e, S[4 * i]), S[4 * i + 1] = fmaf(k.y, e, S[4 * i + 1]);
                 S[4 * i + 2] = fmaf(k.z, e, S[4 * i + 2]), S[4 * i + 3] = fmaf(k.w, e, S[4 * i + 3]);
-                read = fmaf(S[4 * i], q.x, read), read = fmaf(S[4 * i + 1], q.y, read);
-                read = fmaf(S[4 * i + 2], q.z, read), read = fmaf(S[4 * i + 3], q.w, read);
+                s0 = fmaf(S[4 * i], q.x, s0), s1 = fmaf(S[4 * i + 1], q.y, s1);
+                s2 = fmaf(S[4 * i + 2], q.z, s2), s3 = fmaf(S[4 * i + 3], q.w, s3);
             }
+            float read = (s0 + s1) + (s2 + s3);
             for (int o = 1; o < parts; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
             if (live && part == 0) p.out[(long long)(row0 + base + c) * p.heads * V + (long long)h * V + col] = read;
         }
     }
-    if (live) {
 #pragma unroll
-        for (int i = 0; i < SCAN_ROWS; i++)
-            if (part * SCAN_ROWS + i < K) mine[i] = S[i];
+    for (int c = 0; c < KR / 32; c++) {
+#pragma unroll
+        for (int i = 0; i < 32; i++) mine_stage[lane * 33 + i] = S[c * 32 + i];
+        __syncwarp();
+        for (int j = 0; j < 32; j++) {
+            const int cj = warp_col0 + j / parts, ch = (j % parts) * KR + c * 32 + lane;
+            if (cj < V && ch < K) head_state[(long long)cj * K + ch] = mine_stage[j * 33 + lane];
+        }
+        __syncwarp();
     }
+}
+
+template <typename T, int KR>
+static int delta_scan_launch(DeltaScan &p, int n_seqs, cudaStream_t s) {
+    int parts = 1;
+    while (parts * KR < p.key) parts *= 2;
+    p.parts = parts;
+    const int cols = SCAN_THREADS / parts;
+    const size_t smem = (size_t)(3 * SCAN_CHUNK * parts * KR + SCAN_CHUNK * cols + SCAN_CHUNK + (SCAN_THREADS / 32) * 32 * 33) * 4;
+    dim3 grid(n_seqs, p.heads, (p.value + cols - 1) / cols);
+    if (smem > 48 * 1024) {
+        cudaError_t e = abk_allow_shared_memory((const void *)delta_scan_kernel<T, KR>, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+    }
+    abk_launch(delta_scan_kernel<T, KR>, grid, dim3(SCAN_THREADS), smem, s, p);
+    return ABK_LAUNCH_RESULT();
 }
 
 extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, const float *decay_in, const void *beta_in,
@@ -227,30 +348,19 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
                               const int *seq_start, const int *seq_slot, int n_seqs, int heads, int kv_heads, int key,
                               int value, void *stream) {
     if (n_seqs <= 0) return 0;
-    if (key < 1 || key > 8 * SCAN_ROWS) ABK_REFUSE("delta rule: key size %d, the kernel takes 1 to %d", key, 8 * SCAN_ROWS);
+    if (key < 1 || key > 256) ABK_REFUSE("delta rule: key size %d, the kernel takes 1 to 256", key);
     if (kv_heads < 1 || heads % kv_heads) ABK_REFUSE("delta rule: %d heads do not divide into %d key heads", heads, kv_heads);
-    if (heads > 65535) ABK_REFUSE("delta rule: %d heads are more than a grid takes", heads);
+    if (heads > 65535 || value > 65535 * 16) ABK_REFUSE("delta rule: %d heads of %d values are more than a grid takes", heads, value);
     DeltaScan p;
     p.qkv = qkv, p.ld_qkv = ld_qkv, p.decay_in = decay_in, p.beta_in = beta_in, p.ld_beta = ld_beta, p.a_log = a_log;
     p.dt_bias = dt_bias, p.state = state, p.out = out, p.seq_start = seq_start, p.seq_slot = seq_slot;
     p.heads = heads, p.kv_heads = kv_heads, p.key = key, p.value = value;
-    int parts = 1;
-    while (parts * SCAN_ROWS < key) parts *= 2;
-    p.parts = parts;
     p.q_scale = 1.0f / sqrtf((float)key);
-    const int cols = SCAN_THREADS / parts;
-    const size_t smem = (size_t)(3 * SCAN_CHUNK * parts * SCAN_ROWS + SCAN_CHUNK * cols + SCAN_CHUNK) * 4;
-    dim3 grid(n_seqs, heads, (value + cols - 1) / cols);
-    if (grid.z > 65535) ABK_REFUSE("delta rule: value size %d is more than a grid takes", value);
     cudaStream_t s = (cudaStream_t)stream;
-    if (smem > 48 * 1024) {
-        cudaError_t e = abk_allow_shared_memory(dtype == ABK_BF16 ? (const void *)delta_scan_kernel<__nv_bfloat16>
-                                                                  : (const void *)delta_scan_kernel<float>, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    if (dtype == ABK_BF16) abk_launch(delta_scan_kernel<__nv_bfloat16>, grid, dim3(SCAN_THREADS), smem, s, p);
-    else abk_launch(delta_scan_kernel<float>, grid, dim3(SCAN_THREADS), smem, s, p);
-    return ABK_LAUNCH_RESULT();
+    const bool bf = dtype == ABK_BF16;
+    if (key <= 32) return bf ? delta_scan_launch<__nv_bfloat16, 32>(p, n_seqs, s) : delta_scan_launch<float, 32>(p, n_seqs, s);
+    if (key <= 64) return bf ? delta_scan_launch<__nv_bfloat16, 64>(p, n_seqs, s) : delta_scan_launch<float, 64>(p, n_seqs, s);
+    return bf ? delta_scan_launch<__nv_bfloat16, 128>(p, n_seqs, s) : delta_scan_launch<float, 128>(p, n_seqs, s);
 }
 
 // ------------------------------------------------------------------ gated per-head norm

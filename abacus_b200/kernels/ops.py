@@ -363,6 +363,11 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     take none of them."""
     if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights or row:
         assert prepare is None, "q, k and v must be prepared before these kernels"
+        if (exact_weights and batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
+                and n_heads // n_kv_heads <= 16):
+            attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=v_dim,
+                            keep_first=keep_first, sink=sink, row=row)  # one token a sequence: split along the keys
+            return
         if (exact_weights and not batch.is_decode and not batch.any_continuation
                 and attention_window_takes(qkv, head_dim, v_dim or head_dim, n_heads, n_kv_heads, row)):
             attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, v_dim=v_dim,
@@ -412,6 +417,34 @@ def attention_window(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, bat
                                          _i(n_heads * head_dim), _i((n_heads + n_kv_heads) * head_dim), _f(scale),
                                          _i(window or 0), _i(keep_first or 0), _p(sink), _p(batch.seq_start), _i(n_seqs),
                                          _i(max_tiles), _stream()), "attention_window")
+
+
+def attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=None, keep_first=0,
+                    sink=None, row=None, max_keys=None):
+    """One new token per sequence against the paged cache with the general options (see attention_generic), split
+    along the keys into parts of 128 that a second kernel folds (csrc/attention_split.cu); softmax weights float32.
+    max_keys bounds the keys a row sees (by default the window and its kept keys, or the step's position bound)."""
+    _need_cuda(qkv, out, sink)
+    lib = load_module("attention_split")
+    n, vd = batch.n_rows, v_dim or head_dim
+    heads_size = (n_heads + n_kv_heads) * head_dim + n_kv_heads * vd
+    row = row or heads_size
+    assert qkv.is_contiguous() and qkv.shape[1] == row >= heads_size and out.is_contiguous() and out.dtype == qkv.dtype
+    assert out.shape[1] == n_heads * vd and out.shape[0] >= n and cache.k.dtype == qkv.dtype and cache.v.shape[-1] == vd
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads)
+    top = getattr(batch, "position_bound", None) or batch.max_len_after
+    if batch.max_len_after > top:
+        raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {top}")
+    if max_keys is None:
+        max_keys = min(top, window + (keep_first or 0)) if window else top
+    n_parts = -(-max_keys // 128)
+    parts = ws.get("attention_parts", (n * n_heads * n_parts * (vd + 2),), torch.float32)
+    _check(lib, lib.abk_attention_split(
+        _p(qkv), _ll(row), _p(out), _i(_dt(qkv)), _i(n), _i(n_heads), _i(n_kv_heads), _i(head_dim), _i(vd), _f(scale),
+        _i(window or 0), _i(keep_first or 0), _p(sink), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot),
+        _p(cache.k), _p(cache.v), _p(cache.page_table), _i(cache.table_width), _i(cache.ring_pages),
+        _i(cache.pinned_pages), _i(cache.tokens_per_page), _i(max_keys), _p(parts), _ll(parts.numel()), _stream()),
+        "attention_split", kernels=2)
 
 
 PREFILL_ON_MMA = False  # True: head size 128 too runs on the warp-level kernel (for comparison)

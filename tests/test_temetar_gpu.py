@@ -89,11 +89,12 @@ def test_embedding_with_the_pair_table_remembers_the_last_token_of_a_step():
     assert status.tolist() == [0, 0, 0, 0] and remembered.tolist()[3] == seqs[3][-1] and remembered.tolist()[0] == seqs[0][-1]
 
 
-@pytest.mark.parametrize("taps", [1, 2, 4])
-def test_short_convolution_in_portions_of_every_size(taps):
+@pytest.mark.parametrize("taps,C", [(1, 37), (2, 37), (4, 37), (3, 40), (8, 48)])
+def test_short_convolution_in_portions_of_every_size(taps, C):
+    """37 channels go one to a thread, 40 and 48 several to a thread as one vector."""
     from abacus_b200.kernels import ops
     rng = np.random.default_rng(taps)
-    C, ld, T = 37, 48, 23
+    ld, T = 48, 23
     x = rng.standard_normal((T, ld)).astype(np.float32)
     w = rng.standard_normal((C, taps)).astype(np.float32)
     want = plain.silu(plain.short_convolution(x[:, :C], w))
@@ -206,6 +207,8 @@ def test_attention_with_sink_window_and_kept_first_keys_in_prompts_and_decoding(
     in turn; as a prompt from the step's rows and token by token from the paged cache (a ring behind pinned pages)."""
     from abacus_b200.cache import CacheNeed, SequenceCache
     from abacus_b200.kernels import ops
+    from abacus_b200.parts import Workspace
+    ws = Workspace(torch.device(DEV, torch.cuda.current_device()))
     H, G, D, V, window, keep, scale = 4, 2, 16, 24, 70, 5, 0.05
     T = 300  # five pages: the ring of three behind the pinned first page is gone round once
     tol = dict(rtol=2e-4, atol=2e-4) if dtype == torch.float32 else dict(rtol=3e-2, atol=3e-2)
@@ -266,6 +269,8 @@ def test_attention_with_sink_window_and_kept_first_keys_in_prompts_and_decoding(
                     ops.attention_generic(qkv, one, H, G, D, scale, window, b, kv, v_dim=V, keep_first=keep, sink=dev(sink),
                                           exact_weights=True)
                     np.testing.assert_allclose(one.float().cpu().numpy(), want[i:i + 1], err_msg=f"decoded row {i}, loud {loud}", **tol)
+                    ops.attention_split(qkv, one, H, G, D, scale, window, b, kv, ws, v_dim=V, keep_first=keep, sink=dev(sink))
+                    np.testing.assert_allclose(one.float().cpu().numpy(), want[i:i + 1], err_msg=f"decoded row {i} in parts, loud {loud}", **tol)
                 cache.advance(slot, 1)
             cache.close_slot(slot)
 
@@ -296,6 +301,51 @@ def test_the_tensor_core_prompt_kernel_on_unequal_prompts(H, G, D, V, window, ke
     got, want = out.float().cpu().numpy(), np.concatenate(wants)
     # float32 weights: what is left is the rounding of the stored result
     np.testing.assert_allclose(got, want, rtol=2 ** -8, atol=1e-3)
+
+
+@pytest.mark.parametrize("H,G,D,V,window,keep,dtype", [(8, 1, 32, 200, None, 0, torch.bfloat16), (6, 2, 24, 40, 300, 9, torch.float32),
+                                                        (16, 1, 64, 8, 130, 128, torch.bfloat16), (3, 3, 256, 130, 128, 0, torch.bfloat16)])
+def test_decoding_in_parts_in_an_unequal_batch(H, G, D, V, window, keep, dtype):
+    """Rows at very different positions in one decode step, each against the plain formulas: a first token, rows
+    within one part of 128 keys, at its border, and over many parts; groups of up to 16 heads; values beyond 128."""
+    from abacus_b200.cache import CacheNeed, SequenceCache
+    from abacus_b200.kernels import ops
+    from abacus_b200.parts import Workspace
+    ws = Workspace(torch.device(DEV, torch.cuda.current_device()))
+    lens, scale = [1, 500, 128, 129, 77], 0.2
+    need = CacheNeed(n_kv_heads=G, head_dim=D, window=window, v_head_dim=V, keep_first=keep)
+    cache = SequenceCache([need], [None], 64 * 32, dtype, DEV, max_slots=8, max_context=64 * 16)
+    kv = cache.views[0].kv
+    wants, last_rows, slots = [], [], []
+    for i, T in enumerate(lens):
+        q, k, v, sink, _, _ = _attention_case(T, H, G, D, V, window, keep, scale, seed=50 + i)
+        if i == 0:
+            sink0 = sink
+        if dtype == torch.bfloat16:
+            q, k, v = plain.bf16_round(q), plain.bf16_round(k), plain.bf16_round(v)
+        z = np.einsum("ihd,jhd->hij", q, np.repeat(k, H // G, axis=1)) * np.float32(scale)
+        w = plain.softmax_with_sink(z, sink0, plain.visible(T, window or T, keep))
+        wants.append(np.einsum("hij,jhv->ihv", w, np.repeat(v, H // G, axis=1)).reshape(T, H * V)[-1])
+        row = np.concatenate([q.reshape(T, -1), k.reshape(T, -1), v.reshape(T, -1)], axis=1)
+        width = -(-row.shape[1] // 8) * 8
+        row = np.concatenate([row, np.zeros((T, width - row.shape[1]), dtype=np.float32)], axis=1)
+        slot = cache.open_slot()
+        slots.append(slot)
+        if T > 1:  # all but the last token as a prompt: its keys and values into the cache
+            cache.reserve(slot, T - 1)
+            b = batch_of([(slot, [0] * (T - 1), 0)])
+            ops.qkv_prep(dev(row[:-1], dtype), H, G, D, b, None, None, None, None, None, 0, False, kv, v_dim=V, row=width)
+            cache.advance(slot, T - 1)
+        last_rows.append(row[-1])
+    for slot, T in zip(slots, lens):
+        cache.reserve(slot, T)
+    b = batch_of([(slot, [0], T - 1) for slot, T in zip(slots, lens)])
+    qkv = dev(np.stack(last_rows), dtype)
+    ops.qkv_prep(qkv, H, G, D, b, None, None, None, None, None, 0, False, kv, v_dim=V, row=width)
+    out = torch.empty((len(lens), H * V), dtype=dtype, device=DEV)
+    ops.attention_split(qkv, out, H, G, D, scale, window, b, kv, ws, v_dim=V, keep_first=keep, sink=dev(sink0), row=width)
+    tol = dict(rtol=2e-4, atol=2e-4) if dtype == torch.float32 else dict(rtol=2 ** -8, atol=2e-3)
+    np.testing.assert_allclose(out.float().cpu().numpy(), np.stack(wants), **tol)
 
 
 def test_a_large_sink_takes_the_weight_and_no_sink_is_plain_softmax():
