@@ -38,36 +38,43 @@ __device__ __forceinline__ void visible_keys(const AttnSplit &p, int pos, int &l
     total = kept + pos - lo + 1;
 }
 
+// q (float32, 16-byte aligned, the same for every thread: a broadcast) . k (this thread's key row)
 template <typename T> __device__ __forceinline__ float dot_q(const float *q, const T *k, int hd);
 template <> __device__ __forceinline__ float dot_q<float>(const float *q, const float *k, int hd) {
     float acc = 0.0f;
     for (int i = 0; i < hd; i += 4) {
-        float4 v = *(const float4 *)(k + i);
-        acc = fmaf(q[i], v.x, acc), acc = fmaf(q[i + 1], v.y, acc), acc = fmaf(q[i + 2], v.z, acc), acc = fmaf(q[i + 3], v.w, acc);
+        const float4 v = *(const float4 *)(k + i), w = *(const float4 *)(q + i);
+        acc = fmaf(w.x, v.x, acc), acc = fmaf(w.y, v.y, acc), acc = fmaf(w.z, v.z, acc), acc = fmaf(w.w, v.w, acc);
     }
     return acc;
 }
 template <> __device__ __forceinline__ float dot_q<__nv_bfloat16>(const float *q, const __nv_bfloat16 *k, int hd) {
-    float acc = 0.0f;
+    float a0 = 0.0f, a1 = 0.0f;
     for (int i = 0; i < hd; i += 8) {
-        uint4 raw = *(const uint4 *)(k + i);
+        const uint4 raw = *(const uint4 *)(k + i);
+        const float4 w0 = *(const float4 *)(q + i), w1 = *(const float4 *)(q + i + 4);
         const __nv_bfloat162 *h = (const __nv_bfloat162 *)&raw;
-#pragma unroll
-        for (int u = 0; u < 4; u++) {
-            float2 f = __bfloat1622float2(h[u]);
-            acc = fmaf(q[i + 2 * u], f.x, acc), acc = fmaf(q[i + 2 * u + 1], f.y, acc);
-        }
+        const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]), f2 = __bfloat1622float2(h[2]),
+                     f3 = __bfloat1622float2(h[3]);
+        a0 = fmaf(w0.x, f0.x, a0), a1 = fmaf(w0.y, f0.y, a1), a0 = fmaf(w0.z, f1.x, a0), a1 = fmaf(w0.w, f1.y, a1);
+        a0 = fmaf(w1.x, f2.x, a0), a1 = fmaf(w1.y, f2.y, a1), a0 = fmaf(w1.z, f3.x, a0), a1 = fmaf(w1.w, f3.y, a1);
     }
-    return acc;
+    return a0 + a1;
 }
 
-template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_split_kernel(AttnSplit p) {
-    extern __shared__ float as_smem[];
+// STAGED: the part's 128 key rows and value rows come into shared memory by cp.async, all at once (rows of keys padded
+// by 16 bytes so that a thread reading its own row meets no bank conflict); else each thread reads global memory.
+// GMAX: the group's size rounded up to 1, 2, 4, 8 or 16 (what the loops over its heads are unrolled to).
+template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(AS_THREADS) attention_split_kernel(AttnSplit p) {
+    extern __shared__ __align__(16) float as_smem[];
     const int group = p.n_heads / p.n_kv_heads, hd = p.head_dim, vd = p.v_dim;
     float *q_s = as_smem;                      // [group][hd]
     float *p_s = q_s + group * hd;             // [group][128]
     float *red = p_s + group * AS_THREADS;     // [4][group] maxima, then sums
-    __shared__ long long v_off[AS_THREADS];
+    const int k_pitch = hd * (int)sizeof(T) + 16;
+    uint8_t *k_s = (uint8_t *)(red + ((4 * group + 3) & ~3));  // [128][k_pitch]
+    uint8_t *v_s = k_s + AS_THREADS * k_pitch;                 // [128][vd]
+    __shared__ long long k_off[AS_THREADS], v_off[AS_THREADS];
     const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     const int seq = p.token_seq[t];
@@ -76,36 +83,58 @@ template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_sp
     int lo, kept, total;
     visible_keys(p, pos, lo, kept, total);
     if (part * AS_THREADS >= total) return;  // the fold knows how many parts a row has
-    const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)kvh * group * hd;
-    for (int e = tid; e < group * hd; e += AS_THREADS) q_s[e] = to_float(q[e]);
-    __syncthreads();
+    const int n_valid = total - part * AS_THREADS < AS_THREADS ? total - part * AS_THREADS : AS_THREADS;
     const int number = part * AS_THREADS + tid;
     const bool valid = number < total;
-    float sc[AS_MAX_GROUP];
     if (valid) {
         const int j = number < kept ? number : lo + number - kept;
         const int page = cache_page(p.cache, slot, j);
         v_off[tid] = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, vd);
-        const T *k = (const T *)p.k_pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
+        k_off[tid] = cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
+    }
+    const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)kvh * group * hd;
+    for (int e = tid; e < group * hd; e += AS_THREADS) q_s[e] = to_float(q[e]);
+    __syncthreads();
+    if (STAGED) {
+        const uint32_t k_dst = (uint32_t)__cvta_generic_to_shared(k_s), v_dst = (uint32_t)__cvta_generic_to_shared(v_s);
+        const int k_chunks = hd * (int)sizeof(T) / 16, v_chunks = vd * (int)sizeof(T) / 16;
+        for (int e = tid; e < n_valid * k_chunks; e += AS_THREADS) {
+            const int r = e / k_chunks, c = e - r * k_chunks;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(k_dst + r * k_pitch + c * 16),
+                         "l"((const uint8_t *)((const T *)p.k_pool + k_off[r]) + c * 16) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        for (int e = tid; e < n_valid * v_chunks; e += AS_THREADS) {
+            const int r = e / v_chunks, c = e - r * v_chunks;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(v_dst + (r * v_chunks + c) * 16),
+                         "l"((const uint8_t *)((const T *)p.v_pool + v_off[r]) + c * 16) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+        asm volatile("cp.async.wait_group 1;" ::: "memory");  // the keys are here
+        __syncthreads();
+    }
+    float sc[GMAX];
+    if (valid) {
+        const T *k = STAGED ? (const T *)(k_s + tid * k_pitch) : (const T *)p.k_pool + k_off[tid];
 #pragma unroll
-        for (int g = 0; g < AS_MAX_GROUP; g++)
+        for (int g = 0; g < GMAX; g++)
             if (g < group) sc[g] = dot_q<T>(q_s + g * hd, k, hd) * p.scale;
     } else {
 #pragma unroll
-        for (int g = 0; g < AS_MAX_GROUP; g++) sc[g] = -INFINITY;
+        for (int g = 0; g < GMAX; g++) sc[g] = -INFINITY;
     }
     // per head: the part's maximum, the weights against it, their sum
 #pragma unroll
-    for (int g = 0; g < AS_MAX_GROUP; g++) {
+    for (int g = 0; g < GMAX; g++) {
         if (g < group) {
             const float m = warp_max(sc[g]);
             if (lane == 0) red[warp * group + g] = m;
         }
     }
     __syncthreads();
-    float top[AS_MAX_GROUP];
+    float top[GMAX];
 #pragma unroll
-    for (int g = 0; g < AS_MAX_GROUP; g++) {
+    for (int g = 0; g < GMAX; g++) {
         if (g < group) {
             top[g] = fmaxf(fmaxf(red[g], red[group + g]), fmaxf(red[2 * group + g], red[3 * group + g]));
             sc[g] = valid ? expf(sc[g] - top[g]) : 0.0f;
@@ -114,34 +143,36 @@ template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_sp
     }
     __syncthreads();
 #pragma unroll
-    for (int g = 0; g < AS_MAX_GROUP; g++) {
+    for (int g = 0; g < GMAX; g++) {
         if (g < group) {
             const float s = warp_sum(sc[g]);
             if (lane == 0) red[warp * group + g] = s;
         }
     }
+    if (STAGED) asm volatile("cp.async.wait_group 0;" ::: "memory");  // the values are here
     __syncthreads();
     // weighted values: a thread a value column (two for values beyond 128), every head of the group per value read
-    const int n_valid = total - part * AS_THREADS < AS_THREADS ? total - part * AS_THREADS : AS_THREADS;
-    float acc0[AS_MAX_GROUP], acc1[AS_MAX_GROUP];
+    float acc0[GMAX], acc1[GMAX];
 #pragma unroll
-    for (int g = 0; g < AS_MAX_GROUP; g++) acc0[g] = acc1[g] = 0.0f;
+    for (int g = 0; g < GMAX; g++) acc0[g] = acc1[g] = 0.0f;
     const T *v_base = (const T *)p.v_pool;
     if (tid < vd) {
         for (int jj = 0; jj < n_valid; jj++) {
-            const T *v = v_base + v_off[jj];
-            const float a = to_float(v[tid]), b = tid + AS_THREADS < vd ? to_float(v[tid + AS_THREADS]) : 0.0f;
+            const T *v = STAGED ? (const T *)v_s + (long long)jj * vd : v_base + v_off[jj];
+            const float a = to_float(v[tid]);
 #pragma unroll
-            for (int g = 0; g < AS_MAX_GROUP; g++) {
-                if (g < group) {
-                    const float w = p_s[g * AS_THREADS + jj];
-                    acc0[g] = fmaf(w, a, acc0[g]), acc1[g] = fmaf(w, b, acc1[g]);
-                }
+            for (int g = 0; g < GMAX; g++)
+                if (g < group) acc0[g] = fmaf(p_s[g * AS_THREADS + jj], a, acc0[g]);
+            if (tid + AS_THREADS < vd) {
+                const float b = to_float(v[tid + AS_THREADS]);
+#pragma unroll
+                for (int g = 0; g < GMAX; g++)
+                    if (g < group) acc1[g] = fmaf(p_s[g * AS_THREADS + jj], b, acc1[g]);
             }
         }
     }
 #pragma unroll
-    for (int g = 0; g < AS_MAX_GROUP; g++) {
+    for (int g = 0; g < GMAX; g++) {
         if (g < group) {
             float *dst = p.parts + (((long long)t * p.n_heads + kvh * group + g) * p.n_parts + part) * (vd + 2);
             if (tid < vd) dst[tid] = acc0[g];
@@ -212,17 +243,38 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
         ABK_REFUSE("attention_split: the scratch memory holds %lld floats, the step needs %lld", parts_floats,
                    (long long)n_tokens * n_heads * p.n_parts * (v_dim + 2));
     const int group = n_heads / n_kv_heads;
-    const size_t smem = (size_t)(group * head_dim + group * AS_THREADS + 4 * group) * 4;
-    cudaStream_t s = (cudaStream_t)stream;
     const bool bf = dtype == ABK_BF16;
-    if (smem > 48 * 1024) {
-        cudaError_t e = abk_allow_shared_memory(bf ? (const void *)attention_split_kernel<__nv_bfloat16>
-                                                   : (const void *)attention_split_kernel<float>, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
+    const int esize = bf ? 2 : 4;
+    const size_t small = (size_t)(group * head_dim + group * AS_THREADS + ((4 * group + 3) & ~3)) * 4;
+    const size_t staged = small + (size_t)AS_THREADS * (head_dim * esize + 16) + (size_t)AS_THREADS * v_dim * esize;
+    // rows of keys and of values that are whole 16-byte pieces at 16-byte places can be staged in shared memory
+    const bool stage = (head_dim * esize) % 16 == 0 && (v_dim * esize) % 16 == 0 && staged <= 100 * 1024 &&
+                       !(((uintptr_t)k_pool | (uintptr_t)v_pool) & 15);
+    const size_t smem = stage ? staged : small;
+    cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, n_kv_heads, p.n_parts), fold(n_tokens, n_heads);
-    if (bf) abk_launch(attention_split_kernel<__nv_bfloat16>, grid, dim3(AS_THREADS), smem, s, p);
-    else abk_launch(attention_split_kernel<float>, grid, dim3(AS_THREADS), smem, s, p);
+#define SPLIT_LAUNCH(T, STAGED, GMAX)                                                                     \
+    do {                                                                                                  \
+        if (smem > 48 * 1024) {                                                                           \
+            cudaError_t e = abk_allow_shared_memory((const void *)attention_split_kernel<T, STAGED, GMAX>, (int)smem); \
+            if (e != cudaSuccess) return (int)e;                                                          \
+        }                                                                                                 \
+        abk_launch(attention_split_kernel<T, STAGED, GMAX>, grid, dim3(AS_THREADS), smem, s, p);         \
+    } while (0)
+#define SPLIT_BY_GROUP(T, STAGED)                   \
+    do {                                            \
+        if (group <= 1) SPLIT_LAUNCH(T, STAGED, 1); \
+        else if (group <= 2) SPLIT_LAUNCH(T, STAGED, 2); \
+        else if (group <= 4) SPLIT_LAUNCH(T, STAGED, 4); \
+        else if (group <= 8) SPLIT_LAUNCH(T, STAGED, 8); \
+        else SPLIT_LAUNCH(T, STAGED, 16);           \
+    } while (0)
+    if (bf && stage) SPLIT_BY_GROUP(__nv_bfloat16, true);
+    else if (bf) SPLIT_BY_GROUP(__nv_bfloat16, false);
+    else if (stage) SPLIT_BY_GROUP(float, true);
+    else SPLIT_BY_GROUP(float, false);
+#undef SPLIT_BY_GROUP
+#undef SPLIT_LAUNCH
     int rc = ABK_LAUNCH_RESULT();
     if (rc) return rc;
     if (bf) abk_launch(attention_fold_kernel<__nv_bfloat16>, fold, dim3(AS_THREADS), 0, s, p);

@@ -27,6 +27,7 @@ struct ShortConv {
     const float *tail;  // [slots, taps - 1, channels]
     const int *token_seq, *token_pos, *seq_slot, *seq_pos0;
     int channels, taps, n_tokens;
+    int tokens_per_block;  // of the vector kernel: 4 for long steps (its weights read once for four tokens), 1 for short ones
 };
 
 template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(ShortConv p) {
@@ -55,7 +56,8 @@ template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(S
 }
 
 // The same with VEC channels a thread (16 bytes of the storage type), for channel counts and row pitches that are
-// multiples of VEC with everything 16-byte aligned; a block has CONV_TOKENS tokens, its weights read once.
+// multiples of VEC with everything 16-byte aligned, for 2 to 4 taps; a block has CONV_TOKENS tokens, its weights
+// read once, as vectors.
 #define CONV_TOKENS 4
 template <typename T, int VEC> struct ConvVector;
 template <> struct ConvVector<__nv_bfloat16, 8> {
@@ -84,18 +86,20 @@ template <> struct ConvVector<float, 4> {
     static __device__ __forceinline__ void store(float *p, const float *v) { *(float4 *)p = make_float4(v[0], v[1], v[2], v[3]); }
 };
 
-template <typename T, int VEC> __global__ void __launch_bounds__(128) short_conv_vec_kernel(ShortConv p) {
-    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC, taps = p.taps;
-    float w[VEC][CONV_MAX_TAPS];
+template <typename T, int VEC, int TAPS> __global__ void __launch_bounds__(128) short_conv_vec_kernel(ShortConv p) {
+    const int c = (blockIdx.y * blockDim.x + threadIdx.x) * VEC;
+    constexpr int taps = TAPS;
+    float w[VEC * TAPS];  // this thread's weights lie together: VEC channels of TAPS taps, a multiple of 16 bytes
     if (c < p.channels) {
 #pragma unroll
-        for (int u = 0; u < VEC; u++)
-#pragma unroll
-            for (int j = 0; j < CONV_MAX_TAPS; j++) w[u][j] = j < taps ? p.w[(long long)(c + u) * taps + j] : 0.0f;  // weights: ahead of the wait
+        for (int i = 0; i < VEC * TAPS / 4; i++) {
+            const float4 f = *(const float4 *)(p.w + (long long)c * TAPS + 4 * i);  // weights: ahead of the wait
+            w[4 * i] = f.x, w[4 * i + 1] = f.y, w[4 * i + 2] = f.z, w[4 * i + 3] = f.w;
+        }
     }
     pdl_wait();
     if (c >= p.channels) return;
-    for (int t = blockIdx.x * CONV_TOKENS; t < min(p.n_tokens, (blockIdx.x + 1) * CONV_TOKENS); t++) {
+    for (int t = blockIdx.x * p.tokens_per_block; t < min(p.n_tokens, (blockIdx.x + 1) * p.tokens_per_block); t++) {
         T *out = (T *)p.out + (long long)t * p.channels + c;
         const int seq = p.token_seq[t];
         float acc[VEC];
@@ -105,21 +109,19 @@ template <typename T, int VEC> __global__ void __launch_bounds__(128) short_conv
             const int pos = p.token_pos[t], pos0 = p.seq_pos0[seq];
             const float *tail = p.tail + (long long)p.seq_slot[seq] * (taps - 1) * p.channels + c;
 #pragma unroll
-            for (int j = 0; j < CONV_MAX_TAPS; j++) {
-                if (j < taps) {
-                    const int back = taps - 1 - j, at = pos - back;
-                    float v[VEC];
-                    if (at >= pos0) ConvVector<T, VEC>::load((const T *)p.in + (long long)(t - back) * p.ld + c, v);
-                    else if (at >= 0) {
+            for (int j = 0; j < TAPS; j++) {
+                const int back = taps - 1 - j, at = pos - back;
+                float v[VEC];
+                if (at >= pos0) ConvVector<T, VEC>::load((const T *)p.in + (long long)(t - back) * p.ld + c, v);
+                else if (at >= 0) {
 #pragma unroll
-                        for (int u = 0; u < VEC; u++) v[u] = tail[(long long)(at - (pos0 - (taps - 1))) * p.channels + u];
-                    } else {
+                    for (int u = 0; u < VEC; u++) v[u] = tail[(long long)(at - (pos0 - (taps - 1))) * p.channels + u];
+                } else {
 #pragma unroll
-                        for (int u = 0; u < VEC; u++) v[u] = 0.0f;
-                    }
-#pragma unroll
-                    for (int u = 0; u < VEC; u++) acc[u] = fmaf(w[u][j], v[u], acc[u]);
+                    for (int u = 0; u < VEC; u++) v[u] = 0.0f;
                 }
+#pragma unroll
+                for (int u = 0; u < VEC; u++) acc[u] = fmaf(w[u * TAPS + j], v[u], acc[u]);
             }
 #pragma unroll
             for (int u = 0; u < VEC; u++) acc[u] = acc[u] / (1.0f + expf(-acc[u]));
@@ -136,14 +138,19 @@ extern "C" int abk_short_conv(const void *in, long long ld, void *out, int dtype
     ShortConv p;
     p.in = in, p.ld = ld, p.out = out, p.w = w, p.tail = tail, p.token_seq = token_seq, p.token_pos = token_pos;
     p.seq_slot = seq_slot, p.seq_pos0 = seq_pos0, p.channels = channels, p.taps = taps, p.n_tokens = n_tokens;
+    p.tokens_per_block = 1;
     dim3 grid(n_tokens, (channels + 127) / 128);
     if (grid.y > 65535) ABK_REFUSE("short convolution: %d channels are more than a grid takes", channels);
     cudaStream_t s = (cudaStream_t)stream;
     const int vec = dtype == ABK_BF16 ? 8 : 4;
-    if (channels % vec == 0 && ld % vec == 0 && !(((uintptr_t)in | (uintptr_t)out) & 15)) {
-        dim3 tiles((n_tokens + CONV_TOKENS - 1) / CONV_TOKENS, (channels / vec + 127) / 128);
-        if (dtype == ABK_BF16) abk_launch(short_conv_vec_kernel<__nv_bfloat16, 8>, tiles, dim3(128), 0, s, p);
-        else abk_launch(short_conv_vec_kernel<float, 4>, tiles, dim3(128), 0, s, p);
+    if (channels % vec == 0 && ld % vec == 0 && taps >= 2 && taps <= 4 && !(((uintptr_t)in | (uintptr_t)out | (uintptr_t)w) & 15)) {
+        p.tokens_per_block = n_tokens >= 1024 ? CONV_TOKENS : 1;
+        dim3 tiles((n_tokens + p.tokens_per_block - 1) / p.tokens_per_block, (channels / vec + 127) / 128);
+#define CONV_LAUNCH(TAPS)                                                                                          \
+    if (dtype == ABK_BF16) abk_launch(short_conv_vec_kernel<__nv_bfloat16, 8, TAPS>, tiles, dim3(128), 0, s, p); \
+    else abk_launch(short_conv_vec_kernel<float, 4, TAPS>, tiles, dim3(128), 0, s, p);
+        if (taps == 2) { CONV_LAUNCH(2) } else if (taps == 3) { CONV_LAUNCH(3) } else { CONV_LAUNCH(4) }
+#undef CONV_LAUNCH
         return ABK_LAUNCH_RESULT();
     }
     if (dtype == ABK_BF16) abk_launch(short_conv_kernel<__nv_bfloat16>, grid, dim3(128), 0, s, p);
@@ -189,16 +196,22 @@ extern "C" int abk_short_conv_tail(const void *in, long long ld, int dtype, floa
 }
 
 // ------------------------------------------------------------------ the recurrence
-// A thread keeps KR key channels of one value column in registers (KR = 32, 64 or 128: all of a column where the
-// key size allows, else the column's channels are dealt to 2, 4 or 8 neighbouring lanes that meet by shuffles), so
-// the lanes of a warp are different columns and read a token's q, k and g from shared memory at one address (a
-// broadcast). A block has 128 / lanes-per-column columns of one (sequence, head); a chunk of 16 tokens is prepared
-// together (unit vectors, decays, write strengths: a warp a token), then walked in order. The state comes in and
-// goes out through shared memory, so that global memory is read and written in whole lines.
-#define SCAN_CHUNK 16   // tokens prepared together
-#define SCAN_THREADS 128
+// Two kernels. The first prepares every (token, head) in parallel, a warp each: the unit vectors q and k (q times
+// key^-1/2), the decays g, the value row and the write strength b, as one float32 record
+//     [ k | q | g | v (vp) | b, 0, 0, 0 ]     vp = the value size padded to a multiple of 4
+// in which k, q and g each lie as `parts` runs of 32 channels with 4 floats of padding behind each run (zeros
+// beyond the key size; parts = 1, 2, 4 or 8).
+// The second walks each sequence's tokens in order (see delta_scan_kernel): the records of 8 tokens come in by
+// cp.async while the 8 before them are walked. The state comes in and goes out through shared memory, so that global
+// memory is read and written in whole lines.
+#define SCAN_ROWS 32    // key channels a thread keeps
+#define SCAN_RUN 36     // a run of 32 channels with its padding
+#define SCAN_CHUNK 8    // tokens in a stage
 
-struct DeltaScan {
+static inline int delta_parts(int key) { return key <= 32 ? 1 : key <= 64 ? 2 : key <= 128 ? 4 : 8; }
+static inline int delta_record_floats(int key, int value) { return 3 * delta_parts(key) * SCAN_RUN + ((value + 3) & ~3) + 4; }
+
+struct DeltaPrepare {
     const void *qkv;        // [tokens, ld_qkv]: q heads (kv_heads x key), k heads, v heads (heads x value), after the convolution
     long long ld_qkv;
     const float *decay_in;  // [tokens, heads * key]: a, before bias and softplus
@@ -206,161 +219,252 @@ struct DeltaScan {
     long long ld_beta;
     const float *a_log;     // [heads]
     const float *dt_bias;   // [heads * key]
-    float *state;           // [slots, heads, value, key]
-    float *out;             // [tokens, heads * value]
-    const int *seq_start, *seq_slot;
-    int heads, kv_heads, key, value;
-    int parts;              // lanes to a column: 1, 2, 4 or 8; parts * KR >= key
+    float *records;         // [tokens, heads, record]
+    const int *token_seq;
+    long long pairs;        // tokens * heads
+    int heads, kv_heads, key, value, parts, record;
     float q_scale;          // key^-1/2
 };
 
 __device__ __forceinline__ float softplus_f(float z) { return z > 20.0f ? z : log1pf(expf(z)); }
 
-template <typename T, int KR> __global__ void __launch_bounds__(SCAN_THREADS) delta_scan_kernel(DeltaScan p) {
-    extern __shared__ float smem[];
-    const int parts = p.parts, kp = parts * KR;         // padded key size
-    const int cols = SCAN_THREADS / parts;              // columns of this block
-    float *k_s = smem;                                  // [chunk][kp]
-    float *q_s = k_s + SCAN_CHUNK * kp;
-    float *g_s = q_s + SCAN_CHUNK * kp;
-    float *v_s = g_s + SCAN_CHUNK * kp;                 // [chunk][cols]
-    float *b_s = v_s + SCAN_CHUNK * cols;               // [chunk]
-    float *stage = b_s + SCAN_CHUNK;                    // [warps][32 * 33]: 32 floats of each lane, a line at a time
-    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x;
-    const int warp = tid >> 5, lane = tid & 31, n_warps = SCAN_THREADS / 32;
-    const int col = blockIdx.z * cols + tid / parts, part = tid % parts;
-    const int K = p.key, V = p.value;
+template <typename T> __global__ void __launch_bounds__(128) delta_prepare_kernel(DeltaPrepare p) {
+    const long long pair = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    pdl_wait();
+    if (pair >= p.pairs) return;
+    const long long row = pair / p.heads;
+    const int h = (int)(pair - row * p.heads), K = p.key, V = p.value, region = p.parts * SCAN_RUN;
+    float *rec = p.records + pair * p.record;
+    if (p.token_seq[row] < 0) return;  // padding: its record is never read
     const int kvh = h / (p.heads / p.kv_heads);
-    const float decay_rate = expf(p.a_log[h]);  // a weight: ahead of the wait
+    const T *qr = (const T *)p.qkv + row * p.ld_qkv + (long long)kvh * K;
+    const T *kr = qr + (long long)p.kv_heads * K;
+    const T *vr = (const T *)p.qkv + row * p.ld_qkv + 2LL * p.kv_heads * K + (long long)h * V;
+    const float rate = expf(p.a_log[h]);
+    float qq = 0.0f, kk = 0.0f;
+    for (int i = lane; i < K; i += 32) {
+        const float qv = to_float(qr[i]), kv = to_float(kr[i]);
+        qq = fmaf(qv, qv, qq), kk = fmaf(kv, kv, kk);
+    }
+    qq = warp_sum(qq), kk = warp_sum(kk);
+    const float qn = p.q_scale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
+    for (int at = lane; at < region; at += 32) {  // a place within a region: run at / 36, channel at % 36 of it
+        const int i = (at / SCAN_RUN) * SCAN_ROWS + at % SCAN_RUN;
+        const bool real = at % SCAN_RUN < SCAN_ROWS && i < K;
+        rec[at] = real ? to_float(kr[i]) * kn : 0.0f;
+        rec[region + at] = real ? to_float(qr[i]) * qn : 0.0f;
+        rec[2 * region + at] = real ? expf(-rate * softplus_f(p.decay_in[row * p.heads * K + (long long)h * K + i] + p.dt_bias[h * K + i])) : 0.0f;
+    }
+    const int vp = p.record - 3 * region - 4;
+    for (int j = lane; j < vp; j += 32) rec[3 * region + j] = j < V ? to_float(vr[j]) : 0.0f;
+    if (lane < 4) {
+        const float z = to_float(((const T *)p.beta_in)[row * p.ld_beta + h]);
+        rec[3 * region + vp + lane] = lane == 0 ? 1.0f / (1.0f + expf(-z)) : 0.0f;
+    }
+}
+
+struct DeltaScan {
+    const float *records;   // [tokens, heads, record]
+    float *state;           // [slots, heads, value, key]
+    float *out;             // [tokens, heads * value]
+    const int *seq_start, *seq_slot;
+    int heads, key, value, parts, record;
+    int col_warps;          // warps side by side along the columns (each 64 columns): a block has parts * col_warps warps
+};
+
+__device__ __forceinline__ void scan_copy_16(uint32_t dst, const void *src) {
+    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(dst), "l"(src) : "memory");
+}
+
+// A warp has one run of 32 key channels (its part) of 64 value columns, a lane two neighbouring columns: 64 state
+// values in registers. All lanes of a warp read the token's k, q and g of the warp's run at one address. The sums
+// over the key channels meet across the block's warps through shared memory, two barriers a token.
+// MAX_THREADS: the most threads a block has (128, 256 or 512): the fewer, the more registers a thread may use.
+template <int MAX_THREADS> __global__ void __launch_bounds__(MAX_THREADS) delta_scan_kernel(DeltaScan p) {
+    extern __shared__ __align__(16) float smem[];  // records [2][SCAN_CHUNK][R] (before and after the walk: the
+                                                   // state's lines, [warps][32 * 33]), then the partial sums
+    const int parts = p.parts, region = parts * SCAN_RUN, R = p.record, cw = p.col_warps;
+    const int n_warps = parts * cw, n_threads = n_warps * 32;
+    const int seq = blockIdx.x, h = blockIdx.y, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int part = warp % parts, col_warp = warp / parts;
+    const int block_cols = cw * 64, col0 = blockIdx.z * block_cols;          // this block's columns
+    const int local = col_warp * 64 + 2 * lane, col = col0 + local;          // this lane's two columns: col, col + 1
+    const int K = p.key, V = p.value, vp = R - 3 * region - 4;
+    size_t front = (size_t)2 * SCAN_CHUNK * R;
+    if (front < (size_t)n_warps * 32 * 33) front = (size_t)n_warps * 32 * 33;
+    float *sums = smem + ((front + 3) & ~(size_t)3);  // [2 (token parity)][2 (seen, read)][parts][block_cols]
     pdl_wait();
     const int row0 = p.seq_start[seq], n = p.seq_start[seq + 1] - row0;
     if (n <= 0) return;
-    const bool live = col < V;
     float *head_state = p.state + ((long long)p.seq_slot[seq] * p.heads + h) * V * K;
-    float *mine_stage = stage + warp * 32 * 33;
-    // lane j of this warp owns channels [part_j * KR, + KR) of column col_j
-    const int warp_col0 = blockIdx.z * cols + (warp * 32) / parts;
-    float S[KR];
+    float *mine_stage = smem + warp * 32 * 33;  // 32 floats of each of 32 columns, a line at a time
+    float S0[SCAN_ROWS], S1[SCAN_ROWS];
 #pragma unroll
-    for (int c = 0; c < KR / 32; c++) {
+    for (int half = 0; half < 2; half++) {  // the warp's even columns, then its odd ones
+#pragma unroll 8
         for (int j = 0; j < 32; j++) {
-            const int cj = warp_col0 + j / parts, ch = (j % parts) * KR + c * 32 + lane;
+            const int cj = col0 + col_warp * 64 + 2 * j + half, ch = part * SCAN_ROWS + lane;
             mine_stage[j * 33 + lane] = cj < V && ch < K ? head_state[(long long)cj * K + ch] : 0.0f;
         }
         __syncwarp();
 #pragma unroll
-        for (int i = 0; i < 32; i++) S[c * 32 + i] = mine_stage[lane * 33 + i];
+        for (int i = 0; i < SCAN_ROWS; i++) {
+            if (half == 0) S0[i] = mine_stage[lane * 33 + i];
+            else S1[i] = mine_stage[lane * 33 + i];
+        }
         __syncwarp();
     }
+    __syncthreads();  // the records come into the same memory
 
-    for (int base = 0; base < n; base += SCAN_CHUNK) {
+    const uint32_t chunk_s = (uint32_t)__cvta_generic_to_shared(smem);
+    auto fetch = [&](int base, int stage_index) {  // the records of tokens [base, base + count) of this head
         const int count = n - base < SCAN_CHUNK ? n - base : SCAN_CHUNK;
-        __syncthreads();  // the chunk before is done with
-        // a warp prepares a token: unit vectors, decays, the write strength
-        for (int c = warp; c < count; c += n_warps) {
-            const long long row = row0 + base + c;
-            const T *qr = (const T *)p.qkv + row * p.ld_qkv + (long long)kvh * K;
-            const T *kr = qr + (long long)p.kv_heads * K;
-            float qq = 0.0f, kk = 0.0f;
-            for (int i = lane; i < kp; i += 32) {
-                float qv = i < K ? to_float(qr[i]) : 0.0f, kv = i < K ? to_float(kr[i]) : 0.0f;
-                q_s[c * kp + i] = qv, k_s[c * kp + i] = kv;
-                qq = fmaf(qv, qv, qq), kk = fmaf(kv, kv, kk);
-                float g = 0.0f;
-                if (i < K)
-                    g = expf(-decay_rate * softplus_f(p.decay_in[row * p.heads * K + (long long)h * K + i] + p.dt_bias[h * K + i]));
-                g_s[c * kp + i] = g;
-            }
-            qq = warp_sum(qq), kk = warp_sum(kk);
-            const float qn = p.q_scale / sqrtf(qq + 1e-6f), kn = 1.0f / sqrtf(kk + 1e-6f);
-            for (int i = lane; i < kp; i += 32) q_s[c * kp + i] *= qn, k_s[c * kp + i] *= kn;
-            if (lane == 0) {
-                float z = to_float(((const T *)p.beta_in)[row * p.ld_beta + h]);
-                b_s[c] = 1.0f / (1.0f + expf(-z));
-            }
+        const int per = R / 4;
+        for (int e = tid; e < count * per; e += n_threads) {
+            const int c = e / per, q = e - c * per;
+            scan_copy_16(chunk_s + ((stage_index * SCAN_CHUNK + c) * R + q * 4) * 4,
+                         p.records + ((long long)(row0 + base + c) * p.heads + h) * R + q * 4);
         }
-        for (int e = tid; e < count * cols; e += SCAN_THREADS) {
-            const int c = e / cols, j = blockIdx.z * cols + e % cols;
-            const T *vr = (const T *)p.qkv + (long long)(row0 + base + c) * p.ld_qkv + 2LL * p.kv_heads * K + (long long)h * V;
-            v_s[e] = j < V ? to_float(vr[j]) : 0.0f;
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    };
+    fetch(0, 0);
+    int token = 0;
+    for (int base = 0, it = 0; base < n; base += SCAN_CHUNK, it++) {
+        const int count = n - base < SCAN_CHUNK ? n - base : SCAN_CHUNK;
+        if (base + SCAN_CHUNK < n) {  // the next tokens into the other stage (its readers passed the barrier below)
+            fetch(base + SCAN_CHUNK, (it + 1) & 1);
+            asm volatile("cp.async.wait_group 1;" ::: "memory");
+        } else {
+            asm volatile("cp.async.wait_group 0;" ::: "memory");
         }
         __syncthreads();
-        for (int c = 0; c < count; c++) {
-            const float4 *k4 = (const float4 *)(k_s + c * kp + part * KR);
-            const float4 *q4 = (const float4 *)(q_s + c * kp + part * KR);
-            const float4 *g4 = (const float4 *)(g_s + c * kp + part * KR);
-            float s0 = 0.0f, s1 = 0.0f, s2 = 0.0f, s3 = 0.0f;
+        const float *records = smem + (it & 1) * SCAN_CHUNK * R;
+        for (int c = 0; c < count; c++, token++) {
+            const float *rec = records + c * R;
+            const float4 *k4 = (const float4 *)(rec + part * SCAN_RUN);
+            const float4 *q4 = (const float4 *)(rec + region + part * SCAN_RUN);
+            const float4 *g4 = (const float4 *)(rec + 2 * region + part * SCAN_RUN);
+            float *seen_s = sums + (size_t)(token & 1) * 2 * parts * block_cols, *read_s = seen_s + parts * block_cols;
+            float a0 = 0.0f, a1 = 0.0f, b0 = 0.0f, b1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < KR / 4; i++) {
+            for (int i = 0; i < SCAN_ROWS / 4; i++) {
                 const float4 g = g4[i], k = k4[i];
-                S[4 * i] *= g.x, S[4 * i + 1] *= g.y, S[4 * i + 2] *= g.z, S[4 * i + 3] *= g.w;
-                s0 = fmaf(S[4 * i], k.x, s0), s1 = fmaf(S[4 * i + 1], k.y, s1);
-                s2 = fmaf(S[4 * i + 2], k.z, s2), s3 = fmaf(S[4 * i + 3], k.w, s3);
+                S0[4 * i] *= g.x, S0[4 * i + 1] *= g.y, S0[4 * i + 2] *= g.z, S0[4 * i + 3] *= g.w;
+                S1[4 * i] *= g.x, S1[4 * i + 1] *= g.y, S1[4 * i + 2] *= g.z, S1[4 * i + 3] *= g.w;
+                a0 = fmaf(S0[4 * i], k.x, a0), a1 = fmaf(S0[4 * i + 1], k.y, a1);
+                a0 = fmaf(S0[4 * i + 2], k.z, a0), a1 = fmaf(S0[4 * i + 3], k.w, a1);
+                b0 = fmaf(S1[4 * i], k.x, b0), b1 = fmaf(S1[4 * i + 1], k.y, b1);
+                b0 = fmaf(S1[4 * i + 2], k.z, b0), b1 = fmaf(S1[4 * i + 3], k.w, b1);
             }
-            float seen = (s0 + s1) + (s2 + s3);
-            for (int o = 1; o < parts; o <<= 1) seen += __shfl_xor_sync(0xffffffffu, seen, o);
-            const float e = b_s[c] * (v_s[c * cols + tid / parts] - seen);
-            s0 = s1 = s2 = s3 = 0.0f;
+            *(float2 *)(seen_s + part * block_cols + local) = make_float2(a0 + a1, b0 + b1);
+            __syncthreads();
+            float seen0 = 0.0f, seen1 = 0.0f;
+            for (int o = 0; o < parts; o++) {
+                const float2 t = *(const float2 *)(seen_s + o * block_cols + local);
+                seen0 += t.x, seen1 += t.y;
+            }
+            const float beta = rec[3 * region + vp];
+            const float e0 = beta * (rec[3 * region + (col < V ? col : 0)] - seen0);
+            const float e1 = beta * (rec[3 * region + (col + 1 < V ? col + 1 : 0)] - seen1);
+            a0 = a1 = b0 = b1 = 0.0f;
 #pragma unroll
-            for (int i = 0; i < KR / 4; i++) {
+            for (int i = 0; i < SCAN_ROWS / 4; i++) {
                 const float4 k = k4[i], q = q4[i];
-                S[4 * i] = fmaf(k.x, e, S[4 * i]), S[4 * i + 1] = fmaf(k.y, e, S[4 * i + 1]);
-                S[4 * i + 2] = fmaf(k.z, e, S[4 * i + 2]), S[4 * i + 3] = fmaf(k.w, e, S[4 * i + 3]);
-                s0 = fmaf(S[4 * i], q.x, s0), s1 = fmaf(S[4 * i + 1], q.y, s1);
-                s2 = fmaf(S[4 * i + 2], q.z, s2), s3 = fmaf(S[4 * i + 3], q.w, s3);
+                S0[4 * i] = fmaf(k.x, e0, S0[4 * i]), S0[4 * i + 1] = fmaf(k.y, e0, S0[4 * i + 1]);
+                S0[4 * i + 2] = fmaf(k.z, e0, S0[4 * i + 2]), S0[4 * i + 3] = fmaf(k.w, e0, S0[4 * i + 3]);
+                S1[4 * i] = fmaf(k.x, e1, S1[4 * i]), S1[4 * i + 1] = fmaf(k.y, e1, S1[4 * i + 1]);
+                S1[4 * i + 2] = fmaf(k.z, e1, S1[4 * i + 2]), S1[4 * i + 3] = fmaf(k.w, e1, S1[4 * i + 3]);
+                a0 = fmaf(S0[4 * i], q.x, a0), a1 = fmaf(S0[4 * i + 1], q.y, a1);
+                a0 = fmaf(S0[4 * i + 2], q.z, a0), a1 = fmaf(S0[4 * i + 3], q.w, a1);
+                b0 = fmaf(S1[4 * i], q.x, b0), b1 = fmaf(S1[4 * i + 1], q.y, b1);
+                b0 = fmaf(S1[4 * i + 2], q.z, b0), b1 = fmaf(S1[4 * i + 3], q.w, b1);
             }
-            float read = (s0 + s1) + (s2 + s3);
-            for (int o = 1; o < parts; o <<= 1) read += __shfl_xor_sync(0xffffffffu, read, o);
-            if (live && part == 0) p.out[(long long)(row0 + base + c) * p.heads * V + (long long)h * V + col] = read;
+            *(float2 *)(read_s + part * block_cols + local) = make_float2(a0 + a1, b0 + b1);
+            __syncthreads();
+            if (part == 0) {  // the warps of the first run add up what the token reads
+                float r0 = 0.0f, r1 = 0.0f;
+                for (int o = 0; o < parts; o++) {
+                    const float2 t = *(const float2 *)(read_s + o * block_cols + local);
+                    r0 += t.x, r1 += t.y;
+                }
+                float *dst = p.out + (long long)(row0 + base + c) * p.heads * V + (long long)h * V;
+                if (col < V) dst[col] = r0;
+                if (col + 1 < V) dst[col + 1] = r1;
+            }
         }
+        __syncthreads();  // the stage is filled again by the iteration after next (and, at the end, by the state)
     }
 #pragma unroll
-    for (int c = 0; c < KR / 32; c++) {
+    for (int half = 0; half < 2; half++) {
 #pragma unroll
-        for (int i = 0; i < 32; i++) mine_stage[lane * 33 + i] = S[c * 32 + i];
+        for (int i = 0; i < SCAN_ROWS; i++) mine_stage[lane * 33 + i] = half == 0 ? S0[i] : S1[i];
         __syncwarp();
+#pragma unroll 8
         for (int j = 0; j < 32; j++) {
-            const int cj = warp_col0 + j / parts, ch = (j % parts) * KR + c * 32 + lane;
+            const int cj = col0 + col_warp * 64 + 2 * j + half, ch = part * SCAN_ROWS + lane;
             if (cj < V && ch < K) head_state[(long long)cj * K + ch] = mine_stage[j * 33 + lane];
         }
         __syncwarp();
     }
 }
 
-template <typename T, int KR>
-static int delta_scan_launch(DeltaScan &p, int n_seqs, cudaStream_t s) {
-    int parts = 1;
-    while (parts * KR < p.key) parts *= 2;
-    p.parts = parts;
-    const int cols = SCAN_THREADS / parts;
-    const size_t smem = (size_t)(3 * SCAN_CHUNK * parts * KR + SCAN_CHUNK * cols + SCAN_CHUNK + (SCAN_THREADS / 32) * 32 * 33) * 4;
-    dim3 grid(n_seqs, p.heads, (p.value + cols - 1) / cols);
-    if (smem > 48 * 1024) {
-        cudaError_t e = abk_allow_shared_memory((const void *)delta_scan_kernel<T, KR>, (int)smem);
-        if (e != cudaSuccess) return (int)e;
-    }
-    abk_launch(delta_scan_kernel<T, KR>, grid, dim3(SCAN_THREADS), smem, s, p);
-    return ABK_LAUNCH_RESULT();
+// Floats of scratch memory the recurrence needs for n_tokens tokens (its records).
+extern "C" long long abk_delta_scan_scratch(int n_tokens, int heads, int key, int value) {
+    return (long long)n_tokens * heads * delta_record_floats(key, value);
 }
 
 extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, const float *decay_in, const void *beta_in,
                               long long ld_beta, const float *a_log, const float *dt_bias, float *state, float *out,
-                              const int *seq_start, const int *seq_slot, int n_seqs, int heads, int kv_heads, int key,
-                              int value, void *stream) {
-    if (n_seqs <= 0) return 0;
+                              const int *token_seq, const int *seq_start, const int *seq_slot, int n_tokens, int n_seqs,
+                              int heads, int kv_heads, int key, int value, float *records, long long records_floats,
+                              void *stream) {
+    if (n_seqs <= 0 || n_tokens <= 0) return 0;
     if (key < 1 || key > 256) ABK_REFUSE("delta rule: key size %d, the kernel takes 1 to 256", key);
     if (kv_heads < 1 || heads % kv_heads) ABK_REFUSE("delta rule: %d heads do not divide into %d key heads", heads, kv_heads);
     if (heads > 65535 || value > 65535 * 16) ABK_REFUSE("delta rule: %d heads of %d values are more than a grid takes", heads, value);
-    DeltaScan p;
-    p.qkv = qkv, p.ld_qkv = ld_qkv, p.decay_in = decay_in, p.beta_in = beta_in, p.ld_beta = ld_beta, p.a_log = a_log;
-    p.dt_bias = dt_bias, p.state = state, p.out = out, p.seq_start = seq_start, p.seq_slot = seq_slot;
-    p.heads = heads, p.kv_heads = kv_heads, p.key = key, p.value = value;
-    p.q_scale = 1.0f / sqrtf((float)key);
+    const int parts = delta_parts(key), record = delta_record_floats(key, value);
+    if ((long long)n_tokens * heads * record > records_floats || ((uintptr_t)records & 15))
+        ABK_REFUSE("delta rule: the scratch memory holds %lld floats, the step needs %lld (16-byte aligned)", records_floats,
+                   (long long)n_tokens * heads * record);
+    // 64 columns a warp; two warps side by side where they fit a block and the step has (sequence, head) pairs enough
+    // to fill the GPU without the halves of a head going to different SMs
+    const int col_warps = parts <= 4 && value > 64 && (long long)n_seqs * heads * ((value + 63) / 64) > 2LL * abk_sm_count() ? 2 : 1;
+    const int n_warps = parts * col_warps, block_cols = 64 * col_warps;
+    size_t front = (size_t)2 * SCAN_CHUNK * record;
+    if (front < (size_t)n_warps * 32 * 33) front = (size_t)n_warps * 32 * 33;
+    const size_t smem = (((front + 3) & ~(size_t)3) + (size_t)4 * parts * block_cols) * 4;
+    if (smem > 220 * 1024) ABK_REFUSE("delta rule: heads of %d x %d need more shared memory than an SM has", key, value);
     cudaStream_t s = (cudaStream_t)stream;
-    const bool bf = dtype == ABK_BF16;
-    if (key <= 32) return bf ? delta_scan_launch<__nv_bfloat16, 32>(p, n_seqs, s) : delta_scan_launch<float, 32>(p, n_seqs, s);
-    if (key <= 64) return bf ? delta_scan_launch<__nv_bfloat16, 64>(p, n_seqs, s) : delta_scan_launch<float, 64>(p, n_seqs, s);
-    return bf ? delta_scan_launch<__nv_bfloat16, 128>(p, n_seqs, s) : delta_scan_launch<float, 128>(p, n_seqs, s);
+    DeltaPrepare q;
+    q.qkv = qkv, q.ld_qkv = ld_qkv, q.decay_in = decay_in, q.beta_in = beta_in, q.ld_beta = ld_beta, q.a_log = a_log;
+    q.dt_bias = dt_bias, q.records = records, q.token_seq = token_seq, q.pairs = (long long)n_tokens * heads;
+    q.heads = heads, q.kv_heads = kv_heads, q.key = key, q.value = value, q.parts = parts, q.record = record;
+    q.q_scale = 1.0f / sqrtf((float)key);
+    const long long blocks = (q.pairs + 3) / 4;
+    if (blocks > 0x7fffffffLL) ABK_REFUSE("delta rule: %lld (token, head) pairs are more than a grid takes", q.pairs);
+    if (dtype == ABK_BF16) abk_launch(delta_prepare_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, s, q);
+    else abk_launch(delta_prepare_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, q);
+    int rc = ABK_LAUNCH_RESULT();
+    if (rc) return rc;
+    DeltaScan p;
+    p.records = records, p.state = state, p.out = out, p.seq_start = seq_start, p.seq_slot = seq_slot;
+    p.heads = heads, p.key = key, p.value = value, p.parts = parts, p.record = record;
+    p.col_warps = col_warps;
+    dim3 grid(n_seqs, heads, (value + block_cols - 1) / block_cols);
+#define SCAN_LAUNCH(MAXT)                                                                                  \
+    do {                                                                                                   \
+        if (smem > 48 * 1024) {                                                                            \
+            cudaError_t e = abk_allow_shared_memory((const void *)delta_scan_kernel<MAXT>, (int)smem);     \
+            if (e != cudaSuccess) return (int)e;                                                           \
+        }                                                                                                  \
+        abk_launch(delta_scan_kernel<MAXT>, grid, dim3(n_warps * 32), smem, s, p);                         \
+    } while (0)
+    if (n_warps <= 4) SCAN_LAUNCH(128);
+    else if (n_warps <= 8) SCAN_LAUNCH(256);
+    else SCAN_LAUNCH(512);
+#undef SCAN_LAUNCH
+    return ABK_LAUNCH_RESULT();
 }
 
 // ------------------------------------------------------------------ gated per-head norm

@@ -57,10 +57,16 @@ def capturable(model):
     """(single-token steps, steps of several tokens): whether the model's steps may be replayed from captured
     graphs. A captured graph replays device work only: a part whose forward decides anything on the host from the
     step's contents cannot be captured, and parts say so: `capturable = True` on every part for single-token
-    steps; for steps of several tokens also no mixer with `capturable_prompts = False`."""
+    steps; for steps of several tokens also no mixer with `capturable_prompts = False`. The second value is True,
+    False, or "from_start": only steps whose sequences all start at their first token."""
     parts = list(model.parts())
     decode = all(getattr(part, "capturable", False) for part in parts)
-    return decode, decode and all(getattr(part, "capturable_prompts", True) for part in parts)
+    prompts = [getattr(part, "capturable_prompts", True) for part in parts]
+    if not decode or not all(prompts):
+        return decode, False
+    # a part may allow captured prompt steps only where every sequence of the step starts at its first token
+    # ("from_start"): what it decides on the host then holds for every step the graph is replayed for
+    return decode, "from_start" if "from_start" in prompts else True
 
 
 class Engine:
@@ -79,7 +85,7 @@ class Engine:
         decode_graphs, prompt_graphs = capturable(model)
         self.graphs = DecodeGraphs(self) if use_graphs and decode_graphs else None
         prompts = use_graphs and prompt_graphs and os.environ.get("ABACUS_PROMPT_GRAPHS", "1") != "0"
-        self.prompt_graphs = PromptGraphs(self) if prompts else None
+        self.prompt_graphs = PromptGraphs(self, from_start_only=prompt_graphs == "from_start") if prompts else None
         self._step_batch = None
 
     # ------------------------------------------------------------ sequences

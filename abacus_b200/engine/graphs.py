@@ -131,8 +131,10 @@ class PromptGraphs:
     """Captured steps that bring several tokens of some sequence. A shape is captured when it comes by a
     second time; at most `keep` graphs are kept (the least recently used goes)."""
 
-    def __init__(self, engine, keep=16):
-        self.engine, self.keep = engine, keep
+    def __init__(self, engine, keep=16, from_start_only=False):
+        """from_start_only: only steps whose sequences all start at their first token are captured and replayed (a
+        part of the model decides something on the host that holds for such steps alone)."""
+        self.engine, self.keep, self.from_start_only = engine, keep, from_start_only
         self.graphs, self.seen = {}, {}
         self.captured = self.replayed = 0
 
@@ -145,6 +147,8 @@ class PromptGraphs:
         """Whether this step is replayed (or captured now). Steps of one token per sequence are the decode
         graphs' (or run as they are)."""
         if all(len(s.tokens) == 1 for s in sequences):
+            return False
+        if self.from_start_only and any(s.start > 0 for s in sequences):
             return False
         key = self.key(sequences)
         if key in self.graphs:

@@ -799,24 +799,29 @@ def short_conv_tail(x, channels, taps, tail, batch):
                                         _stream()), "short_conv_tail")
 
 
-def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim):
+def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim, ws):
     """The gated delta rule over every sequence of the step, token by token, from and into the slots' states (float32
     [slots, heads, value, key]). qkv [tokens, 2 * kv_heads * key + heads * value]: q, k and v after their convolution;
     decay_in float32 [tokens, heads * key] before bias and softplus; beta_in [tokens, >= heads] (rows of any pitch)
-    before the sigmoid; out float32 [tokens, heads * value], not yet normed."""
+    before the sigmoid; out float32 [tokens, heads * value], not yet normed. Two kernels: every (token, head) is
+    prepared in parallel into scratch memory from ws (a parts.Workspace), then the sequences are walked."""
     _need_cuda(qkv, decay_in, beta_in, a_log, dt_bias, state, out)
     lib = load_module("delta_rule")
-    n_seqs = batch.seq_slot.numel()
-    assert qkv.is_contiguous() and qkv.shape[1] == 2 * n_kv_heads * key_dim + n_heads * value_dim
+    lib.abk_delta_scan_scratch.restype = ctypes.c_longlong
+    n, n_seqs = batch.n_rows, batch.seq_slot.numel()
+    assert qkv.is_contiguous() and qkv.shape[1] == 2 * n_kv_heads * key_dim + n_heads * value_dim and qkv.shape[0] >= n
     assert decay_in.dtype == torch.float32 and decay_in.is_contiguous() and decay_in.shape[1] == n_heads * key_dim
     assert beta_in.dtype == qkv.dtype and beta_in.stride(1) == 1 and beta_in.shape[1] >= n_heads
     assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and dt_bias.numel() == n_heads * key_dim
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, value_dim, key_dim)
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == n_heads * value_dim
+    records = ws.get("delta_records", (int(lib.abk_delta_scan_scratch(_i(n), _i(n_heads), _i(key_dim), _i(value_dim))),),
+                     torch.float32)
     _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _p(beta_in),
-                                   _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.seq_start),
-                                   _p(batch.seq_slot), _i(n_seqs), _i(n_heads), _i(n_kv_heads), _i(key_dim),
-                                   _i(value_dim), _stream()), "delta_scan")
+                                   _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq),
+                                   _p(batch.seq_start), _p(batch.seq_slot), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv_heads),
+                                   _i(key_dim), _i(value_dim), _p(records), _ll(records.numel()), _stream()),
+           "delta_scan", kernels=2)
 
 
 def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps):

@@ -47,11 +47,11 @@ class Attention:
         # the values' size (nothing to pad where values are as large as keys: head_dim is a multiple of 8)
         self.row = -(-(self.q_size + self.kv_size + self.v_size) // 8) * 8
         self.cos = self.sin = None
-        # a step of several tokens of a windowed layer is checked on the host (it may have to be refused): such
-        # steps cannot be replayed from a captured graph; single-token steps can
-        # (so is a step of a layer with the general options: whether it may read its keys from the step's rows is
-        # decided from the step's contents)
-        self.capturable_prompts = s.window is None and not self.general
+        # A step of several tokens of a windowed layer is checked on the host (it may have to be refused): such steps
+        # cannot be replayed from a captured graph; single-token steps can. A layer with the general options decides on
+        # the host whether a step reads its keys from the step's own rows; for steps whose sequences all start at
+        # their first token the answer is always yes, so those may be captured ("from_start").
+        self.capturable_prompts = "from_start" if self.general else s.window is None
         self.lists = AttentionStepPlan(s.n_heads)  # the prefill kernels' tiles and work list, made per step
 
     def step_plans(self):

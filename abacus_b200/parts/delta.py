@@ -105,7 +105,7 @@ class ChannelDelta:
         self.gate_out.forward(proj[:, self.at_gate:self.width], gate, n)
         o = ws.get("delta_o", (n, self.v_size), torch.float32)
         ops.delta_scan(qkv, decay, proj[:, self.at_b:self.at_decay], self.decay_log, self.decay_bias, state, o, batch,
-                       s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim)
+                       s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim, ws)
         normed = ws.get("delta_normed", (n, self.v_size), dt)
         ops.gated_head_norm(o, gate, self.out_norm, normed, n, s.n_heads, s.value_dim, s.norm_eps)
         self.o_proj.forward(normed, out, n)

@@ -139,6 +139,8 @@ def test_delta_rule_whole_in_portions_and_token_by_token(H, G, K, V):
     want = _delta_plain(*ins, H, G, K, V)
     noise = np.abs(want - _delta_plain(*ins, H, G, K, V, real=np.float64)).max()
     qkv, decay_in, beta_in, a_log, bias = ins
+    from abacus_b200.parts import Workspace
+    ws = Workspace(torch.device(DEV, torch.cuda.current_device()))
     for cuts in ([T], [17, 2, 1, 25], [1] * T):
         state = torch.randn((3, H, V, K), device=DEV)
         state[1].zero_()
@@ -147,7 +149,7 @@ def test_delta_rule_whole_in_portions_and_token_by_token(H, G, K, V):
             b = batch_of([(1, [0] * n, at)])
             out = torch.empty((n, H * V), dtype=torch.float32, device=DEV)
             ops.delta_scan(dev(qkv[at:at + n]), dev(decay_in[at:at + n]), dev(beta_in[at:at + n])[:, :H + 3], dev(a_log),
-                           dev(bias), state, out, b, H, G, K, V)
+                           dev(bias), state, out, b, H, G, K, V, ws)
             got.append(out.cpu().numpy())
             at += n
         np.testing.assert_allclose(np.concatenate(got), want, rtol=1e-4, atol=2e-5 + 4 * noise, err_msg=str(cuts[:4]))
@@ -167,8 +169,9 @@ def test_delta_rule_in_an_unequal_batch_and_in_bfloat16_inputs():
     b = batch_of([(slot, [0] * n, 0) for slot, n in zip(slots, lens)])
     cat = lambda j: np.concatenate([i[j] for i in ins])
     out = torch.empty((sum(lens), H * V), dtype=torch.float32, device=DEV)
+    from abacus_b200.parts import Workspace
     ops.delta_scan(dev(cat(0), torch.bfloat16), dev(cat(1)), dev(cat(2), torch.bfloat16), dev(a_log), dev(bias), state, out,
-                   b, H, G, K, V)
+                   b, H, G, K, V, Workspace(torch.device(DEV, torch.cuda.current_device())))
     np.testing.assert_allclose(out.cpu().numpy(), np.concatenate(want), rtol=1e-4, atol=5e-5)
     assert float(state[1].abs().max()) == 0.0 and float(state[2].abs().max()) > 0.0  # only the step's slots are touched
 
