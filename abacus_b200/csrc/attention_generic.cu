@@ -38,7 +38,14 @@ struct AttnGeneric {
     const void *k_step, *v_step;
     long long kv_row;   // elements between rows of k_step / v_step
     PagedCache v_cache; // the values' pool has pages of v_dim
+    int vector_rows;    // key rows are whole 16-byte pieces at 16-byte places (else they are read an element at a time)
 };
+
+template <typename T> __device__ __forceinline__ float dot_row_plain(const float *q, const T *k, int hd) {
+    float acc = 0.0f;
+    for (int i = 0; i < hd; i++) acc = fmaf(q[i], to_float(k[i]), acc);
+    return acc;
+}
 
 template <typename T> __device__ __forceinline__ float dot_row(const float *q, const T *k, int hd);
 template <> __device__ __forceinline__ float dot_row<float>(const float *q, const float *k, int hd) {
@@ -108,7 +115,8 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGene
                 k = (const T *)p.k_pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
             }
             v_off[tid] = vo;
-            s = dot_row<T>(q_s, k, hd) * (ROUNDED_P ? p.scale * 1.4426950408889634f : p.scale);
+            s = (p.vector_rows ? dot_row<T>(q_s, k, hd) : dot_row_plain<T>(q_s, k, hd)) *
+                (ROUNDED_P ? p.scale * 1.4426950408889634f : p.scale);
         }
         float m_new, pj, corr;
         if (ROUNDED_P) {
@@ -157,8 +165,8 @@ extern "C" int abk_attention_general(const void *q, long long q_row, void *out, 
     if (keep_first < 0 || (keep_first > 0 && window <= 0)) keep_first = 0;
     if (sink && !exact_weights && dtype == ABK_BF16)
         ABK_REFUSE("attention: a sink goes with softmax weights in float32 (exact_weights)");
-    if (head_dim > ATT_MAX_HEAD_DIM || head_dim % 8 || head_dim < 8)
-        ABK_REFUSE("attention: head_dim %d is not a multiple of 8 up to %d", head_dim, ATT_MAX_HEAD_DIM);
+    if (head_dim > ATT_MAX_HEAD_DIM || head_dim < 1)
+        ABK_REFUSE("attention: head_dim %d is not 1 to %d", head_dim, ATT_MAX_HEAD_DIM);
     if (n_kv_heads < 1 || n_heads % n_kv_heads)
         ABK_REFUSE("attention: %d query heads do not divide into %d kv heads", n_heads, n_kv_heads);
     if (n_heads > 65535) ABK_REFUSE("attention: %d heads are more than a grid takes", n_heads);
@@ -172,6 +180,9 @@ extern "C" int abk_attention_general(const void *q, long long q_row, void *out, 
     p.v_cache = p.cache;
     p.k_step = k_step, p.v_step = v_step, p.kv_row = kv_row;
     p.v_dim = v_dim, p.keep_first = keep_first, p.sink = sink;
+    const int esize = dtype == ABK_BF16 ? 2 : 4;
+    p.vector_rows = (head_dim * esize) % 16 == 0 && (kv_row * esize) % 16 == 0 &&
+                    !(((uintptr_t)k_pool | (uintptr_t)k_step) & 15);
     dim3 grid(n_tokens, n_heads);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16 && !exact_weights)

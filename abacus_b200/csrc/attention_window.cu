@@ -10,8 +10,8 @@
 // windowed layer's ring of cache pages is not touched. A CTA has 64 query rows of one head (four warps of 16
 // rows) and walks tiles of 64 keys: the tiles that hold kept first keys out of the window's reach, then the
 // window's (or, without a window, all up to the diagonal); tiles no row of the CTA can see are never loaded.
-// Tiles come in by cp.async into rows padded by 16 bytes (ldmatrix without bank conflicts), the next tile while
-// this one is multiplied.
+// Tiles come in by cp.async into rows padded by 16 bytes (ldmatrix without bank conflicts); with two stages the
+// next tile comes in while this one is multiplied.
 //
 // The weights of the second product are float32: each is split into three bfloat16 parts (the value rounded,
 // the remainder rounded, the remainder of that), which together hold its 24 bits, and the product is taken
@@ -37,6 +37,7 @@ struct AttnWindow {
     const float *sink;         // [n_heads] or null
     const int *seq_start;      // [n_seqs + 1]
     int n_seqs;
+    int stages;                // 2: the next tile of keys and values comes in while this one is multiplied; 1: one tile at a time
 };
 
 __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool real) {
@@ -64,8 +65,8 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
     const int d16 = (D + 15) & ~15, v16 = (VD + 15) & ~15;
     const int pitch_k = d16 * 2 + 16, pitch_v = v16 * 2 + 16;
     const uint32_t q_s = (uint32_t)__cvta_generic_to_shared(aw_smem);
-    const uint32_t k_s = q_s + AW_ROWS * pitch_k;            // two stages
-    const uint32_t v_s = k_s + 2 * AW_KEYS * pitch_k;        // two stages
+    const uint32_t k_s = q_s + AW_ROWS * pitch_k;                   // p.stages stages
+    const uint32_t v_s = k_s + p.stages * AW_KEYS * pitch_k;        // p.stages stages
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, c2 = (lane & 3) * 2;
     const int h = blockIdx.y, kvh = h / (p.n_heads / p.n_kv_heads);
     const float sink2 = p.sink ? p.sink[h] * 1.4426950408889634f : -INFINITY;  // a weight: ahead of the wait
@@ -106,14 +107,19 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
     const int row_a = r0 + warp * 16 + g, row_b = row_a + 8;  // the two query rows (positions) this thread has a part of
 
     for (int it = 0; it < n_tiles; it++) {
-        const int stage = it & 1, key0 = TILE_AT(it) * AW_KEYS;
-        if (it + 1 < n_tiles) {  // the next tile into the other stage (its last readers passed the barrier below)
+        const int stage = p.stages == 2 ? it & 1 : 0, key0 = TILE_AT(it) * AW_KEYS;
+        if (p.stages == 2 && it + 1 < n_tiles) {  // the next tile into the other stage (its last readers passed the barrier below)
             const int next = TILE_AT(it + 1) * AW_KEYS;
             load_tile(k_s + (stage ^ 1) * AW_KEYS * pitch_k, pitch_k, d16, kg, p.row, next, n, D);
             load_tile(v_s + (stage ^ 1) * AW_KEYS * pitch_v, pitch_v, v16, vg, p.row, next, n, VD);
             cp_async_commit();
             cp_async_wait<1>();
         } else {
+            if (p.stages == 1 && it > 0) {  // one stage: this tile now (other CTAs of the SM work meanwhile)
+                load_tile(k_s, pitch_k, d16, kg, p.row, key0, n, D);
+                load_tile(v_s, pitch_v, v16, vg, p.row, key0, n, VD);
+                cp_async_commit();
+            }
             cp_async_wait<0>();
         }
         __syncthreads();
@@ -239,7 +245,15 @@ extern "C" int abk_attention_window(const void *qkv, long long row, void *out, i
     p.head_dim = head_dim, p.v_dim = v_dim, p.k_off = k_off, p.v_off = v_off, p.scale_log2 = scale * 1.4426950408889634f;
     p.window = window > 0 ? window : 0, p.keep_first = keep_first, p.sink = sink, p.seq_start = seq_start, p.n_seqs = n_seqs;
     const int d16 = (head_dim + 15) & ~15, v16 = (v_dim + 15) & ~15;
-    const int smem = 3 * 64 * (d16 * 2 + 16) + 2 * 64 * (v16 * 2 + 16);
+    static int stages_env = -1;  // ABACUS_WINDOW_STAGES=1|2 pins the number of stages (for comparison)
+    if (stages_env < 0) {
+        const char *e = getenv("ABACUS_WINDOW_STAGES");
+        stages_env = e && (e[0] == '1' || e[0] == '2') ? e[0] - '0' : 0;
+    }
+    // one stage by default: measured on a B200 (16 heads of 128, window 1,024) a CTA that waits for its tile while the
+    // SM's other CTAs work (four fit) beats two stages with three CTAs an SM: 1,100 against 1,376 us for 8 x 2,048 tokens
+    p.stages = stages_env ? stages_env : 1;
+    const int smem = (1 + p.stages) * 64 * (d16 * 2 + 16) + p.stages * 64 * (v16 * 2 + 16);
     cudaError_t e = abk_allow_shared_memory((const void *)attention_window_kernel, smem);
     if (e != cudaSuccess) return (int)e;
     abk_launch(attention_window_kernel, dim3(max_tiles, n_heads), dim3(AW_THREADS), (size_t)smem, (cudaStream_t)stream, p);

@@ -455,8 +455,8 @@ extern "C" int abk_qkv_prep_general(void *qkv, int dtype, int n_tokens, int n_he
                                     void *v_pool, const int *page_table, int table_width, int ring_pages,
                                     int tokens_per_page, int v_dim, int pinned_pages, long long row_size, void *stream) {
     if (n_tokens <= 0) return 0;
-    if (head_dim > MAX_HEAD_DIM || head_dim < 2 || head_dim % 2)
-        ABK_REFUSE("qkv_prep: head_dim %d is not an even number up to %d", head_dim, MAX_HEAD_DIM);
+    if (head_dim > MAX_HEAD_DIM || head_dim < 1)
+        ABK_REFUSE("qkv_prep: head_dim %d is not 1 to %d", head_dim, MAX_HEAD_DIM);
     if (cos && (rotary_dim < 2 || rotary_dim % 2 || rotary_dim > head_dim))
         ABK_REFUSE("qkv_prep: rotary_dim %d does not fit head_dim %d", rotary_dim, head_dim);
     QkvPrep p;

@@ -364,7 +364,7 @@ def attention(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cac
     if (v_dim or head_dim) != head_dim or keep_first or sink is not None or exact_weights or row:
         assert prepare is None, "q, k and v must be prepared before these kernels"
         if (exact_weights and batch.is_decode and not from_step and ws is not None and qkv.dtype == torch.bfloat16
-                and n_heads // n_kv_heads <= 16):
+                and n_heads // n_kv_heads <= 16 and head_dim % 8 == 0):
             attention_split(qkv, out, n_heads, n_kv_heads, head_dim, scale, window, batch, cache, ws, v_dim=v_dim,
                             keep_first=keep_first, sink=sink, row=row)  # one token a sequence: split along the keys
             return

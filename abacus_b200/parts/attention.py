@@ -31,8 +31,6 @@ class Attention:
         s = self.spec = spec
         if s.n_heads % s.n_kv_heads:
             raise ValueError(f"{s.n_heads} query heads do not divide into {s.n_kv_heads} kv heads")
-        if s.head_dim % 8 or s.head_dim > 256:
-            raise ValueError(f"head_dim {s.head_dim}: the attention kernels take multiples of 8 up to 256")
         self.v_dim = s.v_head_dim or s.head_dim
         if self.v_dim < 1 or self.v_dim > 256:
             raise ValueError(f"v_head_dim {self.v_dim}: the attention kernels take value heads of up to 256")
@@ -40,6 +38,10 @@ class Attention:
             raise ValueError("keep_first goes with a window")
         # what only the general kernel takes: values of another size, kept first keys, a sink, float32 weights
         self.general = self.v_dim != s.head_dim or bool(s.keep_first) or s.sink or s.exact_weights
+        if s.head_dim > 256 or s.head_dim < 1 or (s.head_dim % 8 and not self.general):
+            raise ValueError(f"head_dim {s.head_dim}: the attention kernels take multiples of 8 up to 256 (the general "
+                             "kernel, which a layer with a sink, kept first keys or values of their own size runs on, "
+                             "any size up to 256)")
         self.position = POSITIONS.build(s.position) if s.position is not None else None
         self.q_size, self.kv_size = s.n_heads * s.head_dim, s.n_kv_heads * s.head_dim
         self.v_size = s.n_kv_heads * self.v_dim

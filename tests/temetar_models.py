@@ -48,6 +48,12 @@ CONFIGS = {
           "loop": {"start": 0, "stop": 1, "times": 3},
           "layers": [attention_layer(2, 1, 32, 12, 0.18, mask=(64, 64), ff=64),
                      delta_layer(2, 1, 72, 40, 3, (4, 4))]},
+    # S: sizes that fit no vector: attention heads of 20 with values of 7 (a row of 67, padded), 6 dimensions rotated,
+    #    a window of 5 keeping 1; a delta rule with 5 key channels, values of 3, 5 taps; two streams.
+    "S": {"architecture": "Temetar", "vocab": 61, "width": 40, "norm": {"eps": 1e-5}, "residual_mult": 1.3, "streams": 2,
+          "embedding": {"scale": 0.5, "bigram": {"buckets": 7, "mul_prev": 1000003, "mul_cur": 999983}},
+          "layers": [attention_layer(2, 1, 20, 7, 0.2, rot=(100.0, 6), mask=(5, 1), ff=24),
+                     delta_layer(2, 1, 5, 3, 5, (3, 2))]},
 }
 
 

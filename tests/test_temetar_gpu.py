@@ -386,7 +386,8 @@ def _oracle(raw, tensors, tokens, dtype):
     return want, float(np.abs(want - plain.forward(raw, tensors, tokens)).max())
 
 
-@pytest.mark.parametrize("name,dtype", [("P", "float32"), ("Q", "float32"), ("R", "float32"), ("Q", "bfloat16"), ("R", "bfloat16")])
+@pytest.mark.parametrize("name,dtype", [("P", "float32"), ("Q", "float32"), ("R", "float32"), ("S", "float32"),
+                                        ("Q", "bfloat16"), ("R", "bfloat16"), ("S", "bfloat16")])
 def test_prompts_decoding_batches_and_used_slots_against_the_plain_model(tmp_path, name, dtype):
     engine, raw, tensors, _ = _engine(tmp_path, name, dtype)
     rng = np.random.default_rng(7)
