@@ -44,6 +44,12 @@ __device__ __forceinline__ void cp_async_16(uint32_t dst, const void *src, bool 
     const int bytes = real ? 16 : 0;  // 0: the 16 bytes are filled with zeros
     asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
 }
+// 2^x by the special-function unit (float32, about two units in the last place; -inf gives 0)
+__device__ __forceinline__ float exp2_sfu(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ void cp_async_commit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cp_async_wait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
@@ -143,17 +149,33 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
         }
         // what each row may see, the tile's maximum per row
         const bool kept_tile = it < kept_tiles;  // all its keys lie before every row's window: only kept first keys count
+        // a tile whose every key every row of this warp sees (below the diagonal, inside the window, rows within the
+        // sequence) needs no look at single keys: most tiles of a long window
+        const int warp_first = r0 + warp * 16, warp_last = warp_first + 15;
+        const bool clear = !kept_tile && key0 + AW_KEYS - 1 <= warp_first && warp_last < n &&
+                           (p.window <= 0 || warp_last - key0 < p.window);
         float top[2] = {-INFINITY, -INFINITY};
+        if (clear) {
 #pragma unroll
-        for (int t = 0; t < 8; t++) {
+            for (int t = 0; t < 8; t++) {
 #pragma unroll
-            for (int e = 0; e < 4; e++) {
-                const int j = key0 + t * 8 + c2 + (e & 1), i = e < 2 ? row_a : row_b;
-                bool seen = j <= i && i < n;
-                if (kept_tile) seen = seen && j < p.keep_first;
-                else if (p.window > 0) seen = seen && (i - j < p.window || j < p.keep_first);
-                s[t][e] = seen ? s[t][e] * p.scale_log2 : -INFINITY;
-                top[e >> 1] = fmaxf(top[e >> 1], s[t][e]);
+                for (int e = 0; e < 4; e++) {
+                    s[t][e] *= p.scale_log2;
+                    top[e >> 1] = fmaxf(top[e >> 1], s[t][e]);
+                }
+            }
+        } else {
+#pragma unroll
+            for (int t = 0; t < 8; t++) {
+#pragma unroll
+                for (int e = 0; e < 4; e++) {
+                    const int j = key0 + t * 8 + c2 + (e & 1), i = e < 2 ? row_a : row_b;
+                    bool seen = j <= i && i < n;
+                    if (kept_tile) seen = seen && j < p.keep_first;
+                    else if (p.window > 0) seen = seen && (i - j < p.window || j < p.keep_first);
+                    s[t][e] = seen ? s[t][e] * p.scale_log2 : -INFINITY;
+                    top[e >> 1] = fmaxf(top[e >> 1], s[t][e]);
+                }
             }
         }
         float corr[2], ref[2];
@@ -161,7 +183,7 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
         for (int r = 0; r < 2; r++) {
             const float m_new = fmaxf(m[r], quad_max(top[r]));
             ref[r] = m_new == -INFINITY ? 0.0f : m_new;  // a row that has seen nothing yet: all its weights are 0
-            corr[r] = exp2f(m[r] - ref[r]);              // (0 when m is still -inf)
+            corr[r] = exp2_sfu(m[r] - ref[r]);           // (0 when m is still -inf)
             m[r] = m_new;
         }
         float sum[2] = {0.0f, 0.0f};
@@ -169,7 +191,7 @@ __global__ void __launch_bounds__(AW_THREADS) attention_window_kernel(AttnWindow
         for (int t = 0; t < 8; t++) {
 #pragma unroll
             for (int e = 0; e < 4; e++) {
-                s[t][e] = exp2f(s[t][e] - ref[e >> 1]);
+                s[t][e] = exp2_sfu(s[t][e] - ref[e >> 1]);
                 sum[e >> 1] += s[t][e];
             }
         }
