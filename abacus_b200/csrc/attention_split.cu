@@ -62,8 +62,9 @@ template <> __device__ __forceinline__ float dot_q<__nv_bfloat16>(const float *q
     return a0 + a1;
 }
 
-// STAGED: the part's 128 key rows and value rows come into shared memory by cp.async, all at once (rows of keys padded
-// by 16 bytes so that a thread reading its own row meets no bank conflict); else each thread reads global memory.
+// STAGED: the part's 128 key rows come into shared memory by cp.async, all at once (padded by 16 bytes so that a thread
+// reading its own row meets no bank conflict), and once the scores are made the 128 value rows into the same memory,
+// under the softmax; else each thread reads global memory.
 // GMAX: the group's size rounded up to 1, 2, 4, 8 or 16 (what the loops over its heads are unrolled to).
 template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(AS_THREADS) attention_split_kernel(AttnSplit p) {
     extern __shared__ __align__(16) float as_smem[];
@@ -73,7 +74,7 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
     float *red = p_s + group * AS_THREADS;     // [4][group] maxima, then sums
     const int k_pitch = hd * (int)sizeof(T) + 16;
     uint8_t *k_s = (uint8_t *)(red + ((4 * group + 3) & ~3));  // [128][k_pitch]
-    uint8_t *v_s = k_s + AS_THREADS * k_pitch;                 // [128][vd]
+    uint8_t *v_s = k_s;                                        // [128][vd], once the keys are done with
     __shared__ long long k_off[AS_THREADS], v_off[AS_THREADS];
     const int t = blockIdx.x, kvh = blockIdx.y, part = blockIdx.z, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
@@ -96,21 +97,15 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
     for (int e = tid; e < group * hd; e += AS_THREADS) q_s[e] = to_float(q[e]);
     __syncthreads();
     if (STAGED) {
-        const uint32_t k_dst = (uint32_t)__cvta_generic_to_shared(k_s), v_dst = (uint32_t)__cvta_generic_to_shared(v_s);
-        const int k_chunks = hd * (int)sizeof(T) / 16, v_chunks = vd * (int)sizeof(T) / 16;
+        const uint32_t k_dst = (uint32_t)__cvta_generic_to_shared(k_s);
+        const int k_chunks = hd * (int)sizeof(T) / 16;
         for (int e = tid; e < n_valid * k_chunks; e += AS_THREADS) {
             const int r = e / k_chunks, c = e - r * k_chunks;
             asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(k_dst + r * k_pitch + c * 16),
                          "l"((const uint8_t *)((const T *)p.k_pool + k_off[r]) + c * 16) : "memory");
         }
         asm volatile("cp.async.commit_group;" ::: "memory");
-        for (int e = tid; e < n_valid * v_chunks; e += AS_THREADS) {
-            const int r = e / v_chunks, c = e - r * v_chunks;
-            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(v_dst + (r * v_chunks + c) * 16),
-                         "l"((const uint8_t *)((const T *)p.v_pool + v_off[r]) + c * 16) : "memory");
-        }
-        asm volatile("cp.async.commit_group;" ::: "memory");
-        asm volatile("cp.async.wait_group 1;" ::: "memory");  // the keys are here
+        asm volatile("cp.async.wait_group 0;" ::: "memory");  // the keys are here
         __syncthreads();
     }
     float sc[GMAX];
@@ -132,6 +127,16 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
         }
     }
     __syncthreads();
+    if (STAGED) {  // every thread has read its key row: the values come into the same memory, under the softmax
+        const uint32_t v_dst = (uint32_t)__cvta_generic_to_shared(v_s);
+        const int v_chunks = vd * (int)sizeof(T) / 16;
+        for (int e = tid; e < n_valid * v_chunks; e += AS_THREADS) {
+            const int r = e / v_chunks, c = e - r * v_chunks;
+            asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(v_dst + (r * v_chunks + c) * 16),
+                         "l"((const uint8_t *)((const T *)p.v_pool + v_off[r]) + c * 16) : "memory");
+        }
+        asm volatile("cp.async.commit_group;" ::: "memory");
+    }
     float top[GMAX];
 #pragma unroll
     for (int g = 0; g < GMAX; g++) {
@@ -246,7 +251,9 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
     const bool bf = dtype == ABK_BF16;
     const int esize = bf ? 2 : 4;
     const size_t small = (size_t)(group * head_dim + group * AS_THREADS + ((4 * group + 3) & ~3)) * 4;
-    const size_t staged = small + (size_t)AS_THREADS * (head_dim * esize + 16) + (size_t)AS_THREADS * v_dim * esize;
+    size_t rows = (size_t)AS_THREADS * (head_dim * esize + 16);  // the keys' rows, then the values' in the same place
+    if (rows < (size_t)AS_THREADS * v_dim * esize) rows = (size_t)AS_THREADS * v_dim * esize;
+    const size_t staged = small + rows;
     // rows of keys and of values that are whole 16-byte pieces at 16-byte places can be staged in shared memory
     const bool stage = (head_dim * esize) % 16 == 0 && (v_dim * esize) % 16 == 0 && staged <= 100 * 1024 &&
                        !(((uintptr_t)k_pool | (uintptr_t)v_pool) & 15);
