@@ -28,6 +28,8 @@ struct ShortConv {
     const int *token_seq, *token_pos, *seq_slot, *seq_pos0;
     int channels, taps, n_tokens;
     int tokens_per_block;  // of the vector kernel: 4 for long steps (its weights read once for four tokens), 1 for short ones
+    float *new_tail;       // a step of one token a sequence: the kernel leaves the slot's new tail itself (the thread that
+                           // read a channel's old tail writes its new one); null: short_conv_tail does it
 };
 
 template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(ShortConv p) {
@@ -45,11 +47,13 @@ template <typename T> __global__ void __launch_bounds__(128) short_conv_kernel(S
     const float *w = p.w + (long long)c * taps;
     const float *tail = p.tail + (long long)p.seq_slot[seq] * (taps - 1) * p.channels + c;
     float acc = 0.0f;
+    float *left = p.new_tail ? p.new_tail + (long long)p.seq_slot[seq] * (taps - 1) * p.channels + c : nullptr;
     for (int j = 0; j < taps; j++) {
         const int back = taps - 1 - j, at = pos - back;
         float v = 0.0f;
         if (at >= pos0) v = to_float(((const T *)p.in)[(long long)(t - back) * p.ld + c]);
         else if (at >= 0) v = tail[(long long)(at - (pos0 - (taps - 1))) * p.channels];
+        if (left && j > 0) left[(long long)(j - 1) * p.channels] = v;  // the input `back` tokens ago is back + 1 ago next time
         acc = fmaf(w[j], v, acc);
     }
     *out = from_float<T>(acc / (1.0f + expf(-acc)));
@@ -120,6 +124,11 @@ template <typename T, int VEC, int TAPS> __global__ void __launch_bounds__(128) 
 #pragma unroll
                     for (int u = 0; u < VEC; u++) v[u] = 0.0f;
                 }
+                if (p.new_tail && j > 0) {  // the input `back` tokens ago is back + 1 ago next time
+                    float *left = p.new_tail + (long long)p.seq_slot[seq] * (taps - 1) * p.channels + (long long)(j - 1) * p.channels + c;
+#pragma unroll
+                    for (int u = 0; u < VEC; u++) left[u] = v[u];
+                }
 #pragma unroll
                 for (int u = 0; u < VEC; u++) acc[u] = fmaf(w[u * TAPS + j], v[u], acc[u]);
             }
@@ -130,15 +139,17 @@ template <typename T, int VEC, int TAPS> __global__ void __launch_bounds__(128) 
     }
 }
 
-extern "C" int abk_short_conv(const void *in, long long ld, void *out, int dtype, const float *w, const float *tail,
+// update_tail: every sequence of the step brings one token, and the kernel leaves the slots' new tails itself.
+extern "C" int abk_short_conv(const void *in, long long ld, void *out, int dtype, const float *w, float *tail,
                               const int *token_seq, const int *token_pos, const int *seq_slot, const int *seq_pos0,
-                              int n_tokens, int channels, int taps, void *stream) {
+                              int n_tokens, int channels, int taps, int update_tail, void *stream) {
     if (n_tokens <= 0 || channels <= 0) return 0;
     if (taps < 1 || taps > CONV_MAX_TAPS) ABK_REFUSE("short convolution: %d taps, the kernel takes 1 to %d", taps, CONV_MAX_TAPS);
     ShortConv p;
     p.in = in, p.ld = ld, p.out = out, p.w = w, p.tail = tail, p.token_seq = token_seq, p.token_pos = token_pos;
     p.seq_slot = seq_slot, p.seq_pos0 = seq_pos0, p.channels = channels, p.taps = taps, p.n_tokens = n_tokens;
     p.tokens_per_block = 1;
+    p.new_tail = update_tail && taps > 1 ? tail : nullptr;
     dim3 grid(n_tokens, (channels + 127) / 128);
     if (grid.y > 65535) ABK_REFUSE("short convolution: %d channels are more than a grid takes", channels);
     cudaStream_t s = (cudaStream_t)stream;
@@ -214,7 +225,8 @@ static inline int delta_record_floats(int key, int value) { return 3 * delta_par
 struct DeltaPrepare {
     const void *qkv;        // [tokens, ld_qkv]: q heads (kv_heads x key), k heads, v heads (heads x value), after the convolution
     long long ld_qkv;
-    const float *decay_in;  // [tokens, heads * key]: a, before bias and softplus
+    const float *decay_in;  // row t at decay_in + t * ld_decay, heads * key: a, before bias and softplus
+    long long ld_decay;
     const void *beta_in;    // row t, head h at beta_in[t * ld_beta + h], before the sigmoid
     long long ld_beta;
     const float *a_log;     // [heads]
@@ -254,7 +266,7 @@ template <typename T> __global__ void __launch_bounds__(128) delta_prepare_kerne
         const bool real = at % SCAN_RUN < SCAN_ROWS && i < K;
         rec[at] = real ? to_float(kr[i]) * kn : 0.0f;
         rec[region + at] = real ? to_float(qr[i]) * qn : 0.0f;
-        rec[2 * region + at] = real ? expf(-rate * softplus_f(p.decay_in[row * p.heads * K + (long long)h * K + i] + p.dt_bias[h * K + i])) : 0.0f;
+        rec[2 * region + at] = real ? expf(-rate * softplus_f(p.decay_in[row * p.ld_decay + (long long)h * K + i] + p.dt_bias[h * K + i])) : 0.0f;
     }
     const int vp = p.record - 3 * region - 4;
     for (int j = lane; j < vp; j += 32) rec[3 * region + j] = j < V ? to_float(vr[j]) : 0.0f;
@@ -414,7 +426,7 @@ extern "C" long long abk_delta_scan_scratch(int n_tokens, int heads, int key, in
     return (long long)n_tokens * heads * delta_record_floats(key, value);
 }
 
-extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, const float *decay_in, const void *beta_in,
+extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, const float *decay_in, long long ld_decay, const void *beta_in,
                               long long ld_beta, const float *a_log, const float *dt_bias, float *state, float *out,
                               const int *token_seq, const int *seq_start, const int *seq_slot, int n_tokens, int n_seqs,
                               int heads, int kv_heads, int key, int value, float *records, long long records_floats,
@@ -437,7 +449,7 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
     if (smem > 220 * 1024) ABK_REFUSE("delta rule: heads of %d x %d need more shared memory than an SM has", key, value);
     cudaStream_t s = (cudaStream_t)stream;
     DeltaPrepare q;
-    q.qkv = qkv, q.ld_qkv = ld_qkv, q.decay_in = decay_in, q.beta_in = beta_in, q.ld_beta = ld_beta, q.a_log = a_log;
+    q.qkv = qkv, q.ld_qkv = ld_qkv, q.decay_in = decay_in, q.ld_decay = ld_decay, q.beta_in = beta_in, q.ld_beta = ld_beta, q.a_log = a_log;
     q.dt_bias = dt_bias, q.records = records, q.token_seq = token_seq, q.pairs = (long long)n_tokens * heads;
     q.heads = heads, q.kv_heads = kv_heads, q.key = key, q.value = value, q.parts = parts, q.record = record;
     q.q_scale = 1.0f / sqrtf((float)key);
@@ -468,15 +480,17 @@ extern "C" int abk_delta_scan(const void *qkv, long long ld_qkv, int dtype, cons
 }
 
 // ------------------------------------------------------------------ gated per-head norm
-// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :]); one warp per (token, head).
+// out[t, h, :] = o[t, h, :] / sqrt(mean(o^2) + eps) * w * sigmoid(gate[t, h, :]); one warp per (token, head). A token's
+// gates lie at gate + t * ld_gate.
 template <typename T>
-__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float *o, const float *gate, const float *w, T *out,
-                                                              long long n_heads_total, int value, float eps) {
+__global__ void __launch_bounds__(128) gated_head_norm_kernel(const float *o, const float *gate, long long ld_gate, int heads,
+                                                              const float *w, T *out, long long n_heads_total, int value,
+                                                              float eps) {
     pdl_wait();
     const long long head = (long long)blockIdx.x * 4 + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (head >= n_heads_total) return;
-    const float *src = o + head * value, *gs = gate + head * value;
+    const float *src = o + head * value, *gs = gate + (head / heads) * ld_gate + (head % heads) * value;
     float ss = 0.0f;
     for (int j = lane; j < value; j += 32) ss = fmaf(src[j], src[j], ss);
     ss = warp_sum(ss);
@@ -485,18 +499,18 @@ __global__ void __launch_bounds__(128) gated_head_norm_kernel(const float *o, co
         out[head * value + j] = from_float<T>(src[j] * scale * w[j] * (1.0f / (1.0f + expf(-gs[j]))));
 }
 
-extern "C" int abk_gated_head_norm(const float *o, const float *gate, const float *w, void *out, int dtype, int n_tokens,
-                                   int heads, int value, float eps, void *stream) {
+extern "C" int abk_gated_head_norm(const float *o, const float *gate, long long ld_gate, const float *w, void *out, int dtype,
+                                   int n_tokens, int heads, int value, float eps, void *stream) {
     const long long total = (long long)n_tokens * heads;
     if (total <= 0) return 0;
     const long long blocks = (total + 3) / 4;
     if (blocks > 0x7fffffffLL) ABK_REFUSE("gated norm: %lld heads are more than a grid takes", total);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16)
-        abk_launch(gated_head_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, s, o, gate, w,
+        abk_launch(gated_head_norm_kernel<__nv_bfloat16>, dim3((unsigned)blocks), dim3(128), 0, s, o, gate, ld_gate, heads, w,
                    (__nv_bfloat16 *)out, total, value, eps);
     else
-        abk_launch(gated_head_norm_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, o, gate, w, (float *)out, total,
-                   value, eps);
+        abk_launch(gated_head_norm_kernel<float>, dim3((unsigned)blocks), dim3(128), 0, s, o, gate, ld_gate, heads, w,
+                   (float *)out, total, value, eps);
     return ABK_LAUNCH_RESULT();
 }

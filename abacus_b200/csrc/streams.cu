@@ -105,6 +105,11 @@ template <typename TO> __global__ void __launch_bounds__(256) streams_step_vec_k
         leave_s[threadIdx.x] = p.y ? p.mult * p.leave[threadIdx.x] : 0.0f;
         enter_s[threadIdx.x] = p.enter[threadIdx.x];
     }
+    // a row that the block covers in one turn (width up to 4 x threads): the norm's weights come in ahead of the wait
+    // and what was read stays in registers
+    const bool one_turn = d <= 4 * (int)blockDim.x;
+    float4 w_early = make_float4(1.0f, 1.0f, 1.0f, 1.0f), u_kept = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+    if (one_turn && p.w && 4 * (int)threadIdx.x < d) w_early = *(const float4 *)(p.w + 4 * threadIdx.x);
     pdl_wait();
     __syncthreads();
     const int r = blockIdx.x;
@@ -150,7 +155,8 @@ template <typename TO> __global__ void __launch_bounds__(256) streams_step_vec_k
                 }
             }
         }
-        *(float4 *)(u_s + j) = u;
+        if (one_turn) u_kept = u;
+        else *(float4 *)(u_s + j) = u;
         ss += u.x * u.x + u.y * u.y + u.z * u.z + u.w * u.w;
     }
     TO *o = (TO *)p.out + (long long)r * d;
@@ -160,9 +166,9 @@ template <typename TO> __global__ void __launch_bounds__(256) streams_step_vec_k
         scale = 1.0f / sqrtf(ss / (float)d + p.eps);
     }
     for (int j = 4 * threadIdx.x; j < d; j += 4 * blockDim.x) {  // a thread reads back what it wrote itself
-        const float4 u = *(const float4 *)(u_s + j);
-        float4 w = make_float4(1.0f, 1.0f, 1.0f, 1.0f);
-        if (p.w) w = *(const float4 *)(p.w + j);
+        const float4 u = one_turn ? u_kept : *(const float4 *)(u_s + j);
+        float4 w = w_early;
+        if (p.w && !one_turn) w = *(const float4 *)(p.w + j);
         if (p.w) store4(o + j, w.x * (u.x * scale), w.y * (u.y * scale), w.z * (u.z * scale), w.w * (u.w * scale));
         else store4(o + j, u.x, u.y, u.z, u.w);
     }

@@ -772,11 +772,13 @@ def remember_tokens(batch, remembered):
 
 
 # ------------------------------------------------------------------ the delta-rule mixer (csrc/delta_rule.cu)
-def short_conv(x, channels, weight, tail, out, batch):
+def short_conv(x, channels, weight, tail, out, batch, update_tail=False):
     """out[t, c] = silu(sum_j weight[c, j] * x[position - (taps - 1 - j), c]) over the first `channels` columns of x
     (rows of any pitch), per sequence: zeros before its start, the slot's tail (float32 [slots, taps - 1, channels])
-    before this step's rows."""
+    before this step's rows. update_tail (only where every sequence of the step brings one token): the kernel leaves
+    the slots' new tails itself, and short_conv_tail is not needed."""
     _need_cuda(x, weight, tail, out)
+    assert not update_tail or batch.is_decode
     lib = load_module("delta_rule")
     n, taps = batch.n_rows, weight.shape[1]
     assert x.stride(1) == 1 and x.shape[1] >= channels and out.is_contiguous() and out.shape[1] == channels
@@ -784,7 +786,7 @@ def short_conv(x, channels, weight, tail, out, batch):
     assert tail.dtype == torch.float32 and tail.shape[1:] == (max(taps - 1, 0), channels) and tail.is_contiguous()
     _check(lib, lib.abk_short_conv(_p(x), _ll(x.stride(0)), _p(out), _i(_dt(x)), _p(weight), _p(tail), _p(batch.token_seq),
                                    _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_pos0), _i(n), _i(channels),
-                                   _i(taps), _stream()), "short_conv")
+                                   _i(taps), _i(1 if update_tail else 0), _stream()), "short_conv")
 
 
 def short_conv_tail(x, channels, taps, tail, batch):
@@ -802,7 +804,7 @@ def short_conv_tail(x, channels, taps, tail, batch):
 def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_heads, n_kv_heads, key_dim, value_dim, ws):
     """The gated delta rule over every sequence of the step, token by token, from and into the slots' states (float32
     [slots, heads, value, key]). qkv [tokens, 2 * kv_heads * key + heads * value]: q, k and v after their convolution;
-    decay_in float32 [tokens, heads * key] before bias and softplus; beta_in [tokens, >= heads] (rows of any pitch)
+    decay_in float32 [tokens, heads * key] (rows of any pitch) before bias and softplus; beta_in [tokens, >= heads] (rows of any pitch)
     before the sigmoid; out float32 [tokens, heads * value], not yet normed. Two kernels: every (token, head) is
     prepared in parallel into scratch memory from ws (a parts.Workspace), then the sequences are walked."""
     _need_cuda(qkv, decay_in, beta_in, a_log, dt_bias, state, out)
@@ -810,14 +812,14 @@ def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_head
     lib.abk_delta_scan_scratch.restype = ctypes.c_longlong
     n, n_seqs = batch.n_rows, batch.seq_slot.numel()
     assert qkv.is_contiguous() and qkv.shape[1] == 2 * n_kv_heads * key_dim + n_heads * value_dim and qkv.shape[0] >= n
-    assert decay_in.dtype == torch.float32 and decay_in.is_contiguous() and decay_in.shape[1] == n_heads * key_dim
+    assert decay_in.dtype == torch.float32 and decay_in.stride(1) == 1 and decay_in.shape[1] == n_heads * key_dim
     assert beta_in.dtype == qkv.dtype and beta_in.stride(1) == 1 and beta_in.shape[1] >= n_heads
     assert a_log.dtype == torch.float32 and dt_bias.dtype == torch.float32 and dt_bias.numel() == n_heads * key_dim
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, value_dim, key_dim)
     assert out.dtype == torch.float32 and out.is_contiguous() and out.shape[1] == n_heads * value_dim
     records = ws.get("delta_records", (int(lib.abk_delta_scan_scratch(_i(n), _i(n_heads), _i(key_dim), _i(value_dim))),),
                      torch.float32)
-    _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _p(beta_in),
+    _check(lib, lib.abk_delta_scan(_p(qkv), _ll(qkv.stride(0)), _i(_dt(qkv)), _p(decay_in), _ll(decay_in.stride(0)), _p(beta_in),
                                    _ll(beta_in.stride(0)), _p(a_log), _p(dt_bias), _p(state), _p(out), _p(batch.token_seq),
                                    _p(batch.seq_start), _p(batch.seq_slot), _i(n), _i(n_seqs), _i(n_heads), _i(n_kv_heads),
                                    _i(key_dim), _i(value_dim), _p(records), _ll(records.numel()), _stream()),
@@ -826,11 +828,11 @@ def delta_scan(qkv, decay_in, beta_in, a_log, dt_bias, state, out, batch, n_head
 
 def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps):
     """out[t, h] = o[t, h] / sqrt(mean(o[t, h]^2) + eps) * weight * sigmoid(gate[t, h]); o and gate float32
-    [tokens, heads * value], weight float32 [value]."""
+    [tokens, heads * value] (gate: rows of any pitch), weight float32 [value]."""
     _need_cuda(o, gate, weight, out)
     lib = load_module("delta_rule")
     assert o.dtype == torch.float32 and gate.dtype == torch.float32 and weight.dtype == torch.float32
-    assert o.is_contiguous() and gate.is_contiguous() and out.is_contiguous() and weight.numel() == value_dim
+    assert o.is_contiguous() and gate.stride(1) == 1 and out.is_contiguous() and weight.numel() == value_dim
     assert o.shape[1] == gate.shape[1] == out.shape[1] == n_heads * value_dim
-    _check(lib, lib.abk_gated_head_norm(_p(o), _p(gate), _p(weight), _p(out), _i(_dt(out)), _i(n_tokens), _i(n_heads),
+    _check(lib, lib.abk_gated_head_norm(_p(o), _p(gate), _ll(gate.stride(0)), _p(weight), _p(out), _i(_dt(out)), _i(n_tokens), _i(n_heads),
                                         _i(value_dim), _f(eps), _stream()), "gated_head_norm")

@@ -62,12 +62,13 @@ class ChannelDelta:
         stacked[self.at_gate:self.at_gate + s.gate_rank] = params["gate_in"]
         self.in_proj = Linear(to_device(stacked, ctx, ctx.dtype))
 
-        def widened(w, rank):  # [n, rank] with its columns padded to the stacked product's part
-            padded = torch.zeros((w.shape[0], _up8(rank)), dtype=w.dtype)
-            padded[:, :rank] = w
-            return Linear(to_device(padded, ctx, ctx.dtype))
-        self.decay_out = widened(params["decay_out"], s.decay_rank)
-        self.gate_out = widened(params["gate_out"], s.gate_rank)
+        # the two products that widen the inner vectors as one: their inputs lie side by side in a row of the stacked
+        # product, their matrices on the diagonal of one (the zeros cost a product of a few dozen columns nothing)
+        ra, rg = _up8(s.decay_rank), _up8(s.gate_rank)
+        both = torch.zeros((s.n_heads * s.key_dim + self.v_size, ra + rg), dtype=params["decay_out"].dtype)
+        both[:s.n_heads * s.key_dim, :s.decay_rank] = params["decay_out"]
+        both[s.n_heads * s.key_dim:, ra:ra + s.gate_rank] = params["gate_out"]
+        self.widen = Linear(to_device(both, ctx, ctx.dtype))
         self.conv = to_device(torch.cat([params["conv_q"], params["conv_k"], params["conv_v"]], dim=0), ctx, torch.float32)
         self.decay_log = to_device(params["decay_log"], ctx, torch.float32)
         self.decay_bias = to_device(params["decay_bias"], ctx, torch.float32)
@@ -75,7 +76,7 @@ class ChannelDelta:
         self.o_proj = Linear(to_device(params["wo"], ctx, ctx.dtype))
 
     def step_weights(self):
-        return [self.in_proj.weight, self.decay_out.weight, self.gate_out.weight, self.conv, self.decay_log,
+        return [self.in_proj.weight, self.widen.weight, self.conv, self.decay_log,
                 self.decay_bias, self.out_norm, self.o_proj.weight]
 
     def cache_need(self):
@@ -96,13 +97,13 @@ class ChannelDelta:
         proj = ws.get("delta_proj", (n, self.width), dt)
         self.in_proj.forward(xn, proj, n)
         qkv = ws.get("delta_qkv", (n, self.channels), dt)
-        ops.short_conv(proj, self.channels, self.conv, tail, qkv, batch)
-        if s.conv_taps > 1:
+        # a step of one token a sequence: the convolution leaves the new tails itself (a graph replays one kind of step only)
+        ops.short_conv(proj, self.channels, self.conv, tail, qkv, batch, update_tail=batch.is_decode)
+        if s.conv_taps > 1 and not batch.is_decode:
             ops.short_conv_tail(proj, self.channels, s.conv_taps, tail, batch)
-        decay = ws.get("delta_decay", (n, s.n_heads * s.key_dim), torch.float32)
-        self.decay_out.forward(proj[:, self.at_decay:self.at_gate], decay, n)
-        gate = ws.get("delta_gate", (n, self.v_size), torch.float32)
-        self.gate_out.forward(proj[:, self.at_gate:self.width], gate, n)
+        widened = ws.get("delta_widened", (n, s.n_heads * s.key_dim + self.v_size), torch.float32)
+        self.widen.forward(proj[:, self.at_decay:self.width], widened, n)
+        decay, gate = widened[:, :s.n_heads * s.key_dim], widened[:, s.n_heads * s.key_dim:]
         o = ws.get("delta_o", (n, self.v_size), torch.float32)
         ops.delta_scan(qkv, decay, proj[:, self.at_b:self.at_decay], self.decay_log, self.decay_bias, state, o, batch,
                        s.n_heads, s.n_kv_heads, s.key_dim, s.value_dim, ws)
