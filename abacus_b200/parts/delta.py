@@ -3,8 +3,8 @@
 Per head a float32 state S [key, value], zero at a sequence's start and carried from token to token:
     S <- diag(g) S;   e = b (v - S^T k);   S <- S + k e^T;   o = S^T q
 The mixer owns everything around it: one stacked product for q, k, v, the write strength b and the inner vectors of
-the decay and of the output gate; the short causal convolution and SiLU on q, k and v; the two small products that
-widen the inner vectors; the per-head norm of o with its gate; the output product. Its cache is a state per sequence
+the decay and of the output gate; the short causal convolution and SiLU on q, k and v; the product that widens the two
+inner vectors (their matrices on the diagonal of one); the per-head norm of o with its gate; the output product. Its cache is a state per sequence
 and entry: S, and the last inputs of the convolution. It keeps no keys, so its cost per token does not grow.
 
 Everything that enters the recurrence is float32 (unit vectors, decays, b, the state); q, k, v and the inner vectors
