@@ -33,6 +33,7 @@ class LayerKV:
     tokens_per_page: int
     window: object
     pinned_pages: int = 0  # a windowed group that also keeps a sequence's first pages (they come before the ring)
+    values_in_keys: bool = False  # v is k: a value is the first elements of its key row
 
 
 @dataclass
@@ -57,7 +58,10 @@ class _Group:
         self.book = PageBook(n_pages, tpp, self.ring_pages, self.pinned_pages)
         shape = (len(entries), n_pages, need.n_kv_heads, tpp, need.head_dim)
         self.k = guards.zeros(shape, dtype, device, what="cache keys")  # guard words around the pools
-        self.v = guards.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype, device, what="cache values")
+        if need.values_in_keys:  # one pool: a value is the first v_head_dim elements of its key row
+            self.v = self.k
+        else:
+            self.v = guards.zeros(shape[:-1] + (need.v_head_dim or need.head_dim,), dtype, device, what="cache values")
         # pageable on purpose: a copy from pageable memory is staged before copy_ returns, so the
         # host may rewrite a row (a slot used again) while earlier steps are still in flight
         self.table_host = torch.zeros((max_slots, self.table_width), dtype=torch.int32)
@@ -86,7 +90,8 @@ class SequenceCache:
                 continue
             if need.n_kv_heads > 0:
                 keep_first = need.keep_first if need.window is not None else 0
-                key = (need.n_kv_heads, need.head_dim, need.window, need.v_head_dim or need.head_dim, keep_first)
+                key = (need.n_kv_heads, need.head_dim, need.window, need.v_head_dim or need.head_dim, keep_first,
+                       need.values_in_keys)
                 by_need.setdefault(key, []).append(e)
             if need.state_shape:
                 self.states[e] = guards.zeros((self.max_slots, *need.state_shape), torch.float32, device,
@@ -94,8 +99,8 @@ class SequenceCache:
             if need.states:
                 self.named_states[e] = self._named(need, f"entry {e}")
         self.frame = EntryView(True, None, None, self._named(frame_need, "the frame") if frame_need is not None else {})
-        for (hkv, hd, window, vd, keep_first), entries in by_need.items():
-            g = _Group(CacheNeed(hkv, hd, window, v_head_dim=vd, keep_first=keep_first), entries, self.n_pages,
+        for (hkv, hd, window, vd, keep_first, in_keys), entries in by_need.items():
+            g = _Group(CacheNeed(hkv, hd, window, v_head_dim=vd, keep_first=keep_first, values_in_keys=in_keys), entries, self.n_pages,
                        self.max_slots, self.max_context, dtype, self.device)
             self.groups.append(g)
             for i, e in enumerate(entries):
@@ -118,7 +123,7 @@ class SequenceCache:
         if owner in self._of_entry:
             g, i = self._of_entry[owner]
             kv = LayerKV(g.k[i], g.v[i], g.table, g.table_width, g.ring_pages, TOKENS_PER_PAGE, g.need.window,
-                         g.pinned_pages)
+                         g.pinned_pages, g.need.values_in_keys)
         return EntryView(self.sources[e] is None, kv, self.states.get(owner), self.named_states.get(owner, {}))
 
     # ------------------------------------------------------------ slots
@@ -196,5 +201,5 @@ class SequenceCache:
         return min((g.book.pages.n_free for g in self.groups), default=0)
 
     def bytes(self):
-        total = sum((g.k.numel() + g.v.numel()) * g.k.element_size() for g in self.groups)
+        total = sum((g.k.numel() + (0 if g.need.values_in_keys else g.v.numel())) * g.k.element_size() for g in self.groups)
         return total + sum(s.numel() * 4 for s in self._all_states())

@@ -3,7 +3,8 @@ from .registry import (ConfigError, architecture_names, architecture_of, get_arc
 from .specs import (AttentionSpec, BlockSpec, GatedMLPSpec, ModelSpec, NormSpec, RotarySpec, ScheduleEntry)
 from .qwen3 import Qwen3Config
 from .temetar import TemetarConfig
+from .movarax import MovaraxConfig
 
 __all__ = ["ConfigError", "architecture_names", "architecture_of", "get_architecture", "load_config",
            "read_config_json", "register_architecture", "AttentionSpec", "BlockSpec", "GatedMLPSpec", "ModelSpec",
-           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig"]
+           "NormSpec", "RotarySpec", "ScheduleEntry", "Qwen3Config", "TemetarConfig", "MovaraxConfig"]

@@ -36,6 +36,7 @@ class RotarySpec:
     rotary_dim: int
     pairing: str = "half"
     kind: str = "rotary"
+    exact_angles: bool = False  # the table's angles are made in float64 before their cosines and sines are rounded
 
 
 @dataclass(frozen=True)
@@ -87,6 +88,74 @@ class DeltaRuleSpec:
     norm_eps: float
     unit_eps: float = 1e-6
     kind: str = "channel_delta"
+
+
+@dataclass(frozen=True)
+class LatentAttentionSpec:
+    """Causal attention whose keys and values are kept as one low-rank latent row per token, shared by the heads.
+
+    Per token: q = Wq x laid out head by head as [head_dim plain | rot_dim rotated]; Wd x has rank + rot_dim rows: the
+    first `rank`, normed (w * z / sqrt(mean(z^2) + norm_eps)), are the latent c, the last rot_dim one rotated key part r
+    that every head shares. Head h's key is [Uk_h c | r], its value Uv_h c; the score is scale * (q . k). The cache
+    holds [c | r] alone. position: a RotarySpec over (part of) the rot_dim part. sink: a learned score per head that
+    joins the softmax's denominator once, unscaled, with no key and no value. shares_latents: the entry has no
+    down-projection of its own and reads the cache of the schedule entry it names as its source.
+    """
+    hidden: int
+    n_heads: int
+    head_dim: int
+    rot_dim: int
+    v_head_dim: int
+    rank: int
+    scale: float
+    norm_eps: float
+    position: Optional[RotarySpec]
+    sink: bool = False
+    shares_latents: bool = False
+    kind: str = "latent_attention"
+
+
+@dataclass(frozen=True)
+class DecayAttentionSpec:
+    """A recurrent mixer: linear attention with a fixed decay per head.
+
+    q = silu(Wq x), k = silu(Wk x) (n_heads x key_dim), v = silu(Wv x) (n_heads x value_dim). Per head a float32 state
+    S [key_dim, value_dim], zero at a sequence's start: S <- decay_h S + k v^T; o = S^T q. The heads' outputs, side by
+    side, are normed as one row (w * o / sqrt(mean(o^2) + norm_eps)), multiplied by sigmoid(Wg x) and projected by Wo.
+    """
+    hidden: int
+    n_heads: int
+    key_dim: int
+    value_dim: int
+    decay: tuple
+    norm_eps: float
+    kind: str = "decay_attention"
+
+
+@dataclass(frozen=True)
+class ExpertSpec:
+    """A small feed-forward without a gate: down(act(up(x)))."""
+    inter: int
+    activation: str = "relu_squared"
+
+
+@dataclass(frozen=True)
+class RoutedMLPSpec:
+    """A feed-forward of `experts` small layers of which each token uses `top`, and an optional shared one.
+
+    Router logits z = R x in float32; score "sigmoid": s = sigmoid(z), the `top` largest chosen, weights the chosen s
+    as they are; score "softmax_chosen": the softmax of the chosen logits. weight_on "input": the output is
+    sum_e expert_e(w_e x); "output": sum_e w_e expert_e(x). shared (an ExpertSpec or None) runs for every token and
+    is added.
+    """
+    hidden: int
+    experts: int
+    top: int
+    expert: ExpertSpec
+    shared: Optional[ExpertSpec] = None
+    score: str = "sigmoid"
+    weight_on: str = "input"
+    kind: str = "routed_mlp"
 
 
 @dataclass(frozen=True)

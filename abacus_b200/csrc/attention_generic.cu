@@ -17,7 +17,8 @@
 #include "common.cuh"
 
 #define ATT_THREADS 128
-#define ATT_MAX_HEAD_DIM 256
+#define ATT_MAX_HEAD_DIM 640
+#define ATT_COLS (ATT_MAX_HEAD_DIM / ATT_THREADS)  // value columns a thread may have
 
 struct AttnGeneric {
     const void *q;      // row t, head h at q + (t * q_row + h * head_dim)
@@ -38,6 +39,7 @@ struct AttnGeneric {
     const void *k_step, *v_step;
     long long kv_row;   // elements between rows of k_step / v_step
     PagedCache v_cache; // the values' pool has pages of v_dim
+    int values_in_keys; // a value is the first v_dim elements of its key (one pool, one row per token)
     int vector_rows;    // key rows are whole 16-byte pieces at 16-byte places (else they are read an element at a time)
 };
 
@@ -94,7 +96,9 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGene
     for (int d = tid; d < hd; d += ATT_THREADS) q_s[d] = to_float(q[d]);
     __syncthreads();
 
-    float m = -INFINITY, l = 0.0f, acc0 = 0.0f, acc1 = 0.0f;
+    float m = -INFINITY, l = 0.0f, acc[ATT_COLS];
+#pragma unroll
+    for (int u = 0; u < ATT_COLS; u++) acc[u] = 0.0f;
     if (p.sink) m = p.sink[h], l = 1.0f;  // a key with this score and no value (never with ROUNDED_P)
     // two runs of keys: the kept first ones, then the window (or everything up to the token)
     for (int run = first_end > 0 ? 0 : 1; run < 2; run++)
@@ -107,11 +111,11 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGene
             long long vo;
             if (p.k_step) {
                 long long row = (long long)p.seq_start[seq] + j - p.seq_pos0[seq];
-                vo = row * p.kv_row + (long long)kvh * vd;
+                vo = row * p.kv_row + (long long)kvh * (p.values_in_keys ? hd : vd);
                 k = (const T *)p.k_step + row * p.kv_row + (long long)kvh * hd;
             } else {
                 int page = cache_page(p.cache, slot, j);
-                vo = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, vd);
+                vo = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, p.values_in_keys ? hd : vd);
                 k = (const T *)p.k_pool + cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
             }
             v_off[tid] = vo;
@@ -137,21 +141,25 @@ __global__ void __launch_bounds__(ATT_THREADS) attention_generic_kernel(AttnGene
         m = m_new;
         int n_valid = end - base + 1 < ATT_THREADS ? end - base + 1 : ATT_THREADS;
         const T *v_base = (const T *)(p.k_step ? p.v_step : p.v_pool);
-        acc0 *= corr, acc1 *= corr;
+#pragma unroll
+        for (int u = 0; u < ATT_COLS; u++) acc[u] *= corr;
         if (tid < vd) {
             for (int jj = 0; jj < n_valid; jj++) {
                 const T *v = v_base + v_off[jj];
-                acc0 = fmaf(p_s[jj], to_float(v[tid]), acc0);
-                if (tid + ATT_THREADS < vd) acc1 = fmaf(p_s[jj], to_float(v[tid + ATT_THREADS]), acc1);
+                acc[0] = fmaf(p_s[jj], to_float(v[tid]), acc[0]);
+#pragma unroll
+                for (int u = 1; u < ATT_COLS; u++)
+                    if (tid + u * ATT_THREADS < vd) acc[u] = fmaf(p_s[jj], to_float(v[tid + u * ATT_THREADS]), acc[u]);
             }
         }
         __syncthreads();  // p_s and v_off are rewritten by the next tile
     }
-    if (tid < vd) out[tid] = from_float<T>(acc0 / l);
-    if (tid + ATT_THREADS < vd) out[tid + ATT_THREADS] = from_float<T>(acc1 / l);
+#pragma unroll
+    for (int u = 0; u < ATT_COLS; u++)
+        if (tid + u * ATT_THREADS < vd) out[tid + u * ATT_THREADS] = from_float<T>(acc[u] / l);
 }
 
-extern "C" int abk_attention_general(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+static int attention_general(int values_in_keys, const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
                                      int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
                                      const int *token_pos, const int *seq_slot, const int *seq_start,
                                      const int *seq_pos0, const void *k_pool, const void *v_pool,
@@ -179,7 +187,8 @@ extern "C" int abk_attention_general(const void *q, long long q_row, void *out, 
     p.cache.pinned_pages = pinned_pages;
     p.v_cache = p.cache;
     p.k_step = k_step, p.v_step = v_step, p.kv_row = kv_row;
-    p.v_dim = v_dim, p.keep_first = keep_first, p.sink = sink;
+    p.v_dim = v_dim, p.keep_first = keep_first, p.sink = sink, p.values_in_keys = values_in_keys;
+    if (values_in_keys && v_dim > head_dim) ABK_REFUSE("attention: values of %d inside keys of %d", v_dim, head_dim);
     const int esize = dtype == ABK_BF16 ? 2 : 4;
     p.vector_rows = (head_dim * esize) % 16 == 0 && (kv_row * esize) % 16 == 0 &&
                     !(((uintptr_t)k_pool | (uintptr_t)k_step) & 15);
@@ -192,6 +201,33 @@ extern "C" int abk_attention_general(const void *q, long long q_row, void *out, 
     else
         attention_generic_kernel<float, false><<<grid, ATT_THREADS, 0, s>>>(p);
     return ABK_LAUNCH_RESULT();
+}
+
+extern "C" int abk_attention_general(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+                                     int n_kv_heads, int head_dim, float scale, int window, const int *token_seq,
+                                     const int *token_pos, const int *seq_slot, const int *seq_start,
+                                     const int *seq_pos0, const void *k_pool, const void *v_pool,
+                                     const int *page_table, int table_width, int ring_pages, int tokens_per_page,
+                                     const void *k_step, const void *v_step, long long kv_row, int v_dim,
+                                     int keep_first, int pinned_pages, const float *sink, int exact_weights,
+                                     void *stream) {
+    return attention_general(0, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, scale, window, token_seq,
+                             token_pos, seq_slot, seq_start, seq_pos0, k_pool, v_pool, page_table, table_width, ring_pages,
+                             tokens_per_page, k_step, v_step, kv_row, v_dim, keep_first, pinned_pages, sink, exact_weights,
+                             stream);
+}
+
+// Keys that carry their values: a value is the first v_dim elements of its key row (one pool; with keys from the
+// step's rows, one row). What attention over shared latent rows needs (csrc/latent.cu).
+extern "C" int abk_attention_values_in_keys(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+                                            int n_kv_heads, int head_dim, float scale, const int *token_seq,
+                                            const int *token_pos, const int *seq_slot, const int *seq_start,
+                                            const int *seq_pos0, const void *k_pool, const int *page_table,
+                                            int table_width, int tokens_per_page, int v_dim, const float *sink,
+                                            int exact_weights, void *stream) {
+    return attention_general(1, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, scale, 0, token_seq,
+                             token_pos, seq_slot, seq_start, seq_pos0, k_pool, k_pool, page_table, table_width, 0,
+                             tokens_per_page, nullptr, nullptr, 0, v_dim, 0, 0, sink, exact_weights, stream);
 }
 
 // The same without the options: values as large as keys, no kept first keys, no sink, probabilities in the model's type.

@@ -29,6 +29,7 @@ struct AttnSplit {
     const void *k_pool, *v_pool;
     PagedCache cache, v_cache;
     int n_parts;
+    int values_in_keys;  // a value is the first v_dim elements of its key row (one pool)
 };
 
 // (first key of the window, number of kept first keys before it, number of visible keys) of a token at pos
@@ -90,7 +91,7 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
     if (valid) {
         const int j = number < kept ? number : lo + number - kept;
         const int page = cache_page(p.cache, slot, j);
-        v_off[tid] = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, vd);
+        v_off[tid] = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, p.values_in_keys ? hd : vd);
         k_off[tid] = cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
     }
     const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)kvh * group * hd;
@@ -127,7 +128,7 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
         }
     }
     __syncthreads();
-    if (STAGED) {  // every thread has read its key row: the values come into the same memory, under the softmax
+    if (STAGED && !p.values_in_keys) {  // every thread has read its key row: the values come into the same memory, under the softmax
         const uint32_t v_dst = (uint32_t)__cvta_generic_to_shared(v_s);
         const int v_chunks = vd * (int)sizeof(T) / 16;
         for (int e = tid; e < n_valid * v_chunks; e += AS_THREADS) {
@@ -154,7 +155,7 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
             if (lane == 0) red[warp * group + g] = s;
         }
     }
-    if (STAGED) asm volatile("cp.async.wait_group 0;" ::: "memory");  // the values are here
+    if (STAGED && !p.values_in_keys) asm volatile("cp.async.wait_group 0;" ::: "memory");  // the values are here
     __syncthreads();
     // weighted values: a thread a value column (two for values beyond 128), every head of the group per value read
     float acc0[GMAX], acc1[GMAX];
@@ -163,7 +164,8 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
     const T *v_base = (const T *)p.v_pool;
     if (tid < vd) {
         for (int jj = 0; jj < n_valid; jj++) {
-            const T *v = STAGED ? (const T *)v_s + (long long)jj * vd : v_base + v_off[jj];
+            const T *v = !STAGED ? v_base + v_off[jj]
+                         : p.values_in_keys ? (const T *)(k_s + jj * k_pitch) : (const T *)v_s + (long long)jj * vd;
             const float a = to_float(v[tid]);
 #pragma unroll
             for (int g = 0; g < GMAX; g++)
@@ -222,7 +224,7 @@ template <typename T> __global__ void __launch_bounds__(AS_THREADS) attention_fo
 
 // max_keys: an upper bound of the keys any row of the step sees (its position + 1, or window + keep_first);
 // parts: float32 scratch of at least tokens * heads * ceil(max_keys / 128) * (v_dim + 2).
-extern "C" int abk_attention_split(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+static int attention_split(int values_in_keys, const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
                                    int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
                                    const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
                                    const void *k_pool, const void *v_pool, const int *page_table, int table_width,
@@ -243,6 +245,8 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
     p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
     p.v_cache = p.cache;
     p.n_parts = (max_keys + AS_THREADS - 1) / AS_THREADS;
+    p.values_in_keys = values_in_keys;
+    if (values_in_keys && v_dim > head_dim) ABK_REFUSE("attention_split: values of %d inside keys of %d", v_dim, head_dim);
     if (p.n_parts > 65535) ABK_REFUSE("attention_split: %d keys are more than a grid takes", max_keys);
     if ((long long)n_tokens * n_heads * p.n_parts * (v_dim + 2) > parts_floats)
         ABK_REFUSE("attention_split: the scratch memory holds %lld floats, the step needs %lld", parts_floats,
@@ -252,10 +256,10 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
     const int esize = bf ? 2 : 4;
     const size_t small = (size_t)(group * head_dim + group * AS_THREADS + ((4 * group + 3) & ~3)) * 4;
     size_t rows = (size_t)AS_THREADS * (head_dim * esize + 16);  // the keys' rows, then the values' in the same place
-    if (rows < (size_t)AS_THREADS * v_dim * esize) rows = (size_t)AS_THREADS * v_dim * esize;
+    if (!values_in_keys && rows < (size_t)AS_THREADS * v_dim * esize) rows = (size_t)AS_THREADS * v_dim * esize;
     const size_t staged = small + rows;
     // rows of keys and of values that are whole 16-byte pieces at 16-byte places can be staged in shared memory
-    const bool stage = (head_dim * esize) % 16 == 0 && (v_dim * esize) % 16 == 0 && staged <= 100 * 1024 &&
+    const bool stage = (head_dim * esize) % 16 == 0 && (values_in_keys || (v_dim * esize) % 16 == 0) && staged <= 100 * 1024 &&
                        !(((uintptr_t)k_pool | (uintptr_t)v_pool) & 15);
     const size_t smem = stage ? staged : small;
     cudaStream_t s = (cudaStream_t)stream;
@@ -287,4 +291,28 @@ extern "C" int abk_attention_split(const void *q, long long q_row, void *out, in
     if (bf) abk_launch(attention_fold_kernel<__nv_bfloat16>, fold, dim3(AS_THREADS), 0, s, p);
     else abk_launch(attention_fold_kernel<float>, fold, dim3(AS_THREADS), 0, s, p);
     return ABK_LAUNCH_RESULT();
+}
+
+extern "C" int abk_attention_split(const void *q, long long q_row, void *out, int dtype, int n_tokens, int n_heads,
+                                   int n_kv_heads, int head_dim, int v_dim, float scale, int window, int keep_first,
+                                   const float *sink, const int *token_seq, const int *token_pos, const int *seq_slot,
+                                   const void *k_pool, const void *v_pool, const int *page_table, int table_width,
+                                   int ring_pages, int pinned_pages, int tokens_per_page, int max_keys, float *parts,
+                                   long long parts_floats, void *stream) {
+    return attention_split(0, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, window, keep_first,
+                           sink, token_seq, token_pos, seq_slot, k_pool, v_pool, page_table, table_width, ring_pages,
+                           pinned_pages, tokens_per_page, max_keys, parts, parts_floats, stream);
+}
+
+// Keys that carry their values (a value is the first v_dim elements of its key row; one pool): attention over shared
+// latent rows (csrc/latent.cu), every query head in the one group.
+extern "C" int abk_attention_split_values_in_keys(const void *q, long long q_row, void *out, int dtype, int n_tokens,
+                                                  int n_heads, int n_kv_heads, int head_dim, int v_dim, float scale,
+                                                  const float *sink, const int *token_seq, const int *token_pos,
+                                                  const int *seq_slot, const void *k_pool, const int *page_table,
+                                                  int table_width, int tokens_per_page, int max_keys, float *parts,
+                                                  long long parts_floats, void *stream) {
+    return attention_split(1, q, q_row, out, dtype, n_tokens, n_heads, n_kv_heads, head_dim, v_dim, scale, 0, 0, sink,
+                           token_seq, token_pos, seq_slot, k_pool, k_pool, page_table, table_width, 0, 0, tokens_per_page,
+                           max_keys, parts, parts_floats, stream);
 }

@@ -1,0 +1,199 @@
+// A feed-forward of routed experts: every token goes through `top` of `experts` small feed-forward layers, chosen by
+// a router.
+//
+//   moe_route       per token: router logits z = R x in float32 (x as stored), the `top` largest (a tie goes to the
+//                   lower index), and each chosen expert's weight: sigmoid(z) (score 0) or its softmax over the
+//                   chosen (score 1). A pair is (token, k-th choice), numbered token * top + k; pairs of padding rows
+//                   carry expert -1.
+//   routed_product  out[pair] = act(W[expert of pair] (scale of pair * x[row of pair])): a product whose matrix is
+//                   chosen per row. With a scale the input is multiplied by it and rounded to its stored type first
+//                   (the weight acts on the expert's input). A CTA stages the pair's row in shared memory; a warp makes
+//                   an output feature at a time, lanes along the inner dimension, so the expert's rows stream
+//                   coalesced. Float32 sums in a fixed order.
+//   moe_combine     out[t] (+)= sum over k of pairs[t * top + k], in the order of k.
+//   relu_squared    x = max(x, 0)^2 in place.
+#define ABK_DEFINE_ERROR
+#include "common.cuh"
+
+template <typename T>
+__global__ void __launch_bounds__(128) moe_route_kernel(const T *x, long long ldx, const float *router, int d, int experts,
+                                                        int top, int softmax_chosen, const int *token_seq, int *pair_expert,
+                                                        float *pair_weight) {
+    extern __shared__ float mr_smem[];  // [d] the row, [experts] logits, [experts] taken flags
+    float *xs = mr_smem, *z = xs + d;
+    int *taken = (int *)(z + experts);
+    const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    pdl_wait();
+    if (token_seq[t] < 0) {
+        for (int k = tid; k < top; k += 128) pair_expert[(long long)t * top + k] = -1, pair_weight[(long long)t * top + k] = 0.0f;
+        return;
+    }
+    for (int i = tid; i < d; i += 128) xs[i] = to_float(x[(long long)t * ldx + i]);
+    for (int e = tid; e < experts; e += 128) taken[e] = 0;
+    __syncthreads();
+    for (int e = warp; e < experts; e += 4) {
+        const float *r = router + (long long)e * d;
+        float acc = 0.0f;
+        for (int i = lane; i < d; i += 32) acc = fmaf(r[i], xs[i], acc);
+        acc = warp_sum(acc);
+        if (lane == 0) z[e] = acc;
+    }
+    __syncthreads();
+    if (warp != 0) return;
+    float chosen_max = -INFINITY, denom = 0.0f;
+    for (int k = 0; k < top; k++) {
+        float best = -INFINITY;
+        int at = 0x7fffffff;
+        for (int e = lane; e < experts; e += 32)
+            if (!taken[e] && (z[e] > best || at == 0x7fffffff)) best = z[e], at = e;  // (the first of a lane's own is its lowest)
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            const float ob = __shfl_xor_sync(0xffffffffu, best, o);
+            const int oa = __shfl_xor_sync(0xffffffffu, at, o);
+            if (oa != 0x7fffffff && (at == 0x7fffffff || ob > best || (ob == best && oa < at))) best = ob, at = oa;
+        }
+        if (k == 0) chosen_max = best;
+        denom += expf(best - chosen_max);
+        if (lane == 0) {
+            taken[at] = 1;
+            pair_expert[(long long)t * top + k] = at;
+            pair_weight[(long long)t * top + k] = softmax_chosen ? best : 1.0f / (1.0f + expf(-best));
+        }
+        __syncwarp();
+    }
+    if (softmax_chosen && lane == 0)
+        for (int k = 0; k < top; k++) {
+            float *w = pair_weight + (long long)t * top + k;
+            *w = expf(*w - chosen_max) / denom;
+        }
+}
+
+extern "C" int abk_moe_route(const void *x, long long ldx, int dtype, const float *router, int n_tokens, int d, int experts,
+                             int top, int softmax_chosen, const int *token_seq, int *pair_expert, float *pair_weight,
+                             void *stream) {
+    if (n_tokens <= 0) return 0;
+    if (top < 1 || top > experts) ABK_REFUSE("moe_route: %d of %d experts", top, experts);
+    const size_t smem = (size_t)(d + 2 * experts) * 4;
+    if (smem > 200 * 1024) ABK_REFUSE("moe_route: a row of %d and %d experts do not fit shared memory", d, experts);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dtype == ABK_BF16) {
+        if (smem > 48 * 1024) {
+            cudaError_t e = abk_allow_shared_memory((const void *)moe_route_kernel<__nv_bfloat16>, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        abk_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, s, (const __nv_bfloat16 *)x, ldx, router,
+                   d, experts, top, softmax_chosen, token_seq, pair_expert, pair_weight);
+    } else {
+        if (smem > 48 * 1024) {
+            cudaError_t e = abk_allow_shared_memory((const void *)moe_route_kernel<float>, (int)smem);
+            if (e != cudaSuccess) return (int)e;
+        }
+        abk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (const float *)x, ldx, router, d, experts, top,
+                   softmax_chosen, token_seq, pair_expert, pair_weight);
+    }
+    return ABK_LAUNCH_RESULT();
+}
+
+#define RP_PER_WARP 4
+enum { RP_NONE = 0, RP_RELU_SQUARED = 1 };
+
+template <typename T, typename TO, int ACT>
+__global__ void __launch_bounds__(128) routed_product_kernel(const T *__restrict__ x, long long ldx, int pairs_per_row,
+                                                             const T *__restrict__ w, const int *pair_expert,
+                                                             const float *pair_scale, TO *__restrict__ out, long long ldo,
+                                                             int in, int outs) {
+    extern __shared__ float rp_x[];  // [in]
+    const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    pdl_wait();
+    const int e = pair_expert[pair];
+    const int o0 = (blockIdx.y * 4 + warp) * RP_PER_WARP;
+    if (e < 0) {  // a padding row
+        if (lane < RP_PER_WARP && o0 + lane < outs) out[(long long)pair * ldo + o0 + lane] = from_float<TO>(0.0f);
+        return;
+    }
+    const T *row = x + (long long)(pair / pairs_per_row) * ldx;
+    if (pair_scale) {
+        const float sc = pair_scale[pair];
+        for (int i = threadIdx.x; i < in; i += 128) rp_x[i] = to_float(from_float<T>(sc * to_float(row[i])));
+    } else {
+        for (int i = threadIdx.x; i < in; i += 128) rp_x[i] = to_float(row[i]);
+    }
+    __syncthreads();
+    for (int u = 0; u < RP_PER_WARP; u++) {
+        const int o = o0 + u;
+        if (o >= outs) break;
+        const T *wr = w + ((long long)e * outs + o) * in;
+        float acc = 0.0f;
+        for (int i = lane; i < in; i += 32) acc = fmaf(to_float(wr[i]), rp_x[i], acc);
+        acc = warp_sum(acc);
+        if (ACT == RP_RELU_SQUARED) acc = acc > 0.0f ? acc * acc : 0.0f;
+        if (lane == 0) out[(long long)pair * ldo + o] = from_float<TO>(acc);
+    }
+}
+
+// x: the row of pair p is x + (p / pairs_per_row) * ldx (pairs_per_row 1: a row per pair; `top`: a row per token);
+// w [experts][outs][in] of x's type; out [pairs][ldo] of x's type or (out_f32) float32.
+extern "C" int abk_routed_product(const void *x, long long ldx, int pairs_per_row, int dtype, const void *w,
+                                  const int *pair_expert, const float *pair_scale, void *out, long long ldo, int out_f32,
+                                  int activation, int n_pairs, int in, int outs, void *stream) {
+    if (n_pairs <= 0 || outs <= 0) return 0;
+    if (in < 1 || (size_t)in * 4 > 200 * 1024) ABK_REFUSE("routed_product: an inner size of %d does not fit shared memory", in);
+    if (pairs_per_row < 1) pairs_per_row = 1;
+    dim3 grid(n_pairs, (outs + 4 * RP_PER_WARP - 1) / (4 * RP_PER_WARP));
+    if (grid.y > 65535) ABK_REFUSE("routed_product: %d output features are more than a grid takes", outs);
+    const size_t smem = (size_t)in * 4;
+    cudaStream_t s = (cudaStream_t)stream;
+    typedef __nv_bfloat16 bf;
+#define RP_LAUNCH(T, TO, ACT)                                                                                       \
+    do {                                                                                                            \
+        if (smem > 48 * 1024) {                                                                                     \
+            cudaError_t e = abk_allow_shared_memory((const void *)routed_product_kernel<T, TO, ACT>, (int)smem);    \
+            if (e != cudaSuccess) return (int)e;                                                                    \
+        }                                                                                                           \
+        abk_launch(routed_product_kernel<T, TO, ACT>, grid, dim3(128), smem, s, (const T *)x, ldx, pairs_per_row,   \
+                   (const T *)w, pair_expert, pair_scale, (TO *)out, ldo, in, outs);                                \
+    } while (0)
+    const bool relu2 = activation == RP_RELU_SQUARED;
+    if (activation != RP_NONE && !relu2) ABK_REFUSE("routed_product: activation %d is not built", activation);
+    if (dtype == ABK_BF16 && out_f32) { if (relu2) RP_LAUNCH(bf, float, 1); else RP_LAUNCH(bf, float, 0); }
+    else if (dtype == ABK_BF16) { if (relu2) RP_LAUNCH(bf, bf, 1); else RP_LAUNCH(bf, bf, 0); }
+    else { if (relu2) RP_LAUNCH(float, float, 1); else RP_LAUNCH(float, float, 0); }
+#undef RP_LAUNCH
+    return ABK_LAUNCH_RESULT();
+}
+
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float *pairs, float *out, long long total, int d, int top,
+                                                          int add) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const long long t = i / d, j = i - t * d;
+    float acc = pairs[(t * top) * d + j];
+    for (int k = 1; k < top; k++) acc += pairs[(t * top + k) * d + j];
+    out[i] = add ? out[i] + acc : acc;
+}
+
+// out float32 [tokens][d]; pairs float32 [tokens * top][d]; add: out already holds what the pairs join (a shared expert).
+extern "C" int abk_moe_combine(const float *pairs, float *out, int n_tokens, int d, int top, int add, void *stream) {
+    const long long total = (long long)n_tokens * d;
+    if (total <= 0) return 0;
+    abk_launch(moe_combine_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, pairs, out,
+               total, d, top, add);
+    return ABK_LAUNCH_RESULT();
+}
+
+template <typename T> __global__ void __launch_bounds__(256) relu_squared_kernel(T *x, long long total) {
+    pdl_wait();
+    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
+    if (i >= total) return;
+    const float v = to_float(x[i]);
+    x[i] = from_float<T>(v > 0.0f ? v * v : 0.0f);
+}
+
+extern "C" int abk_relu_squared(void *x, int dtype, long long total, void *stream) {
+    if (total <= 0) return 0;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    if (dtype == ABK_BF16) abk_launch(relu_squared_kernel<__nv_bfloat16>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (__nv_bfloat16 *)x, total);
+    else abk_launch(relu_squared_kernel<float>, dim3(blocks), dim3(256), 0, (cudaStream_t)stream, (float *)x, total);
+    return ABK_LAUNCH_RESULT();
+}

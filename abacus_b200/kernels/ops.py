@@ -836,3 +836,185 @@ def gated_head_norm(o, gate, weight, out, n_tokens, n_heads, value_dim, eps):
     assert o.shape[1] == gate.shape[1] == out.shape[1] == n_heads * value_dim
     _check(lib, lib.abk_gated_head_norm(_p(o), _p(gate), _ll(gate.stride(0)), _p(weight), _p(out), _i(_dt(out)), _i(n_tokens), _i(n_heads),
                                         _i(value_dim), _f(eps), _stream()), "gated_head_norm")
+
+
+# ------------------------------------------------------------------ latent attention (csrc/latent.cu)
+def latent_prep(proj, down_at, n_heads, dim, rot, rank, rot_dims, norm_w, eps, cos, sin, q_dst, q_head, q_rot_at, copy_plain,
+                cache, batch):
+    """What stands between the projections of a latent-attention layer and its attention kernel, per token: the
+    latent c = norm_w * z / sqrt(mean(z^2) + eps) over the first `rank` columns of the down-projection (proj[:,
+    down_at:]), the rotation (pairs (2i, 2i+1) of the first rot_dims elements) of the shared key part behind it and of
+    every query head's rotated part (proj[:, h * (dim + rot) + dim:]), the row [c | r | zeros] written to the cache
+    (cache: a cache.LayerKV whose rows hold at least rank + rot elements; None: the entry reads another's cache), and
+    the query parts put into q_dst: head h of a row at h * q_head, its rotated part at + q_rot_at (zeros behind it up
+    to the head's end), its plain part (copy_plain) at + 0."""
+    _need_cuda(proj, norm_w, cos, sin, q_dst)
+    lib = load_module("latent")
+    n = batch.n_rows
+    assert proj.stride(1) == 1 and q_dst.stride(1) == 1 and q_dst.dtype == proj.dtype and proj.shape[0] >= n
+    assert cos is None or (cos.dtype == torch.float32 and cos.shape == sin.shape and cos.shape[1] == rot_dims // 2)
+    if cos is not None and batch.max_position >= cos.shape[0]:
+        raise KernelError(f"position {batch.max_position} is beyond the rotary table of {cos.shape[0]} positions")
+    if cos is None:
+        rot_dims = 0
+    if cache is not None:
+        assert cache.k.dtype == proj.dtype and cache.k.shape[1] == 1 and cache.ring_pages == 0 and cache.k.is_contiguous()
+        assert norm_w.dtype == torch.float32 and norm_w.numel() == rank
+    _check(lib, lib.abk_latent_prep(
+        _p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(n), _i(down_at), _i(n_heads), _i(dim), _i(rot), _i(rank),
+        _i(rot_dims), _p(norm_w), _f(eps), _p(cos), _p(sin), _p(q_dst), _ll(q_dst.stride(0)), _i(q_head), _i(q_rot_at),
+        _i(1 if copy_plain else 0), _p(cache.k if cache is not None else None),
+        _i(cache.k.shape[-1] if cache is not None else 0), _p(cache.page_table if cache is not None else None),
+        _i(cache.table_width if cache is not None else 0), _i(cache.tokens_per_page if cache is not None else 1),
+        _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _stream()), "latent_prep")
+
+
+def head_product(x, x_head, w, out, o_head, n):
+    """out[t, h * o_head + o] = sum_i w[h, o, i] * x[t, h * x_head + i] for t < n: a product per head with a matrix of
+    its own, w [heads, outs, in]; x, w and out of one type, rows of any pitch."""
+    _need_cuda(x, w, out)
+    lib = load_module("latent")
+    heads, outs, inner = w.shape
+    assert x.dtype == w.dtype == out.dtype and w.is_contiguous() and x.stride(1) == 1 and out.stride(1) == 1
+    assert x.shape[0] >= n and out.shape[0] >= n and x_head >= inner and o_head >= outs
+    assert x.shape[1] >= (heads - 1) * x_head + inner and out.shape[1] >= (heads - 1) * o_head + outs
+    _check(lib, lib.abk_head_product(_p(x), _ll(x.stride(0)), _i(x_head), _p(w), _p(out), _ll(out.stride(0)), _i(o_head),
+                                     _i(_dt(x)), _i(n), _i(heads), _i(inner), _i(outs), _stream()), "head_product")
+
+
+def latent_rows(cache, rows, count, batch):
+    """rows[t, :count] = the first `count` elements of the cache row of the step's token t (cache: a cache.LayerKV
+    with one kv head)."""
+    _need_cuda(rows)
+    lib = load_module("latent")
+    assert rows.dtype == cache.k.dtype and rows.stride(1) == 1 and rows.shape[0] >= batch.n_rows and cache.ring_pages == 0
+    _check(lib, lib.abk_latent_rows(_p(cache.k), _i(cache.k.shape[-1]), _p(cache.page_table), _i(cache.table_width),
+                                    _i(cache.tokens_per_page), _p(rows), _ll(rows.stride(0)), _i(count), _i(_dt(rows)),
+                                    _i(batch.n_rows), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot),
+                                    _stream()), "latent_rows")
+
+
+def spread_shared(shared, keys, k_head, at, count, heads, n):
+    """keys[t, h * k_head + at + i] = shared[t, i] for every head h and i < count: a key part that the heads share,
+    copied behind each head's own part."""
+    _need_cuda(shared, keys)
+    lib = load_module("latent")
+    assert shared.dtype == keys.dtype and shared.stride(1) == 1 and keys.stride(1) == 1
+    assert shared.shape[1] >= count and keys.shape[1] >= (heads - 1) * k_head + at + count
+    _check(lib, lib.abk_spread_shared(_p(shared), _ll(shared.stride(0)), _p(keys), _ll(keys.stride(0)), _i(k_head), _i(at),
+                                      _i(count), _i(heads), _i(_dt(keys)), _i(n), _stream()), "spread_shared")
+
+
+def attention_values_in_keys(q, out, n_heads, head_dim, v_dim, scale, batch, cache, sink=None, ws=None):
+    """Causal attention of every token of the step over a cache with one kv head whose values are the first v_dim
+    elements of its keys (latent rows), float32 softmax weights, an optional sink. q [tokens, n_heads * head_dim], out
+    [tokens, n_heads * v_dim]. A step of one token a sequence in bfloat16 with up to 16 heads and rows of up to 256
+    runs split along the keys (csrc/attention_split.cu), everything else on the general kernel."""
+    _need_cuda(q, out, sink)
+    n = batch.n_rows
+    assert q.is_contiguous() and q.shape[1] == n_heads * head_dim and out.is_contiguous() and out.dtype == q.dtype
+    assert out.shape[1] == n_heads * v_dim and cache.k.dtype == q.dtype and cache.k.shape[1:] == (1, cache.tokens_per_page, head_dim)
+    assert cache.values_in_keys and cache.ring_pages == 0 and v_dim <= head_dim
+    assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads)
+    if (batch.is_decode and ws is not None and q.dtype == torch.bfloat16 and n_heads <= 16 and head_dim % 8 == 0
+            and head_dim <= 256):
+        lib = load_module("attention_split")
+        top = getattr(batch, "position_bound", None) or batch.max_len_after
+        if batch.max_len_after > top:
+            raise KernelError(f"a row at position {batch.max_len_after - 1} is beyond the bound {top}")
+        n_parts = -(-top // 128)
+        parts = ws.get("attention_parts", (n * n_heads * n_parts * (v_dim + 2),), torch.float32)
+        _check(lib, lib.abk_attention_split_values_in_keys(
+            _p(q), _ll(q.shape[1]), _p(out), _i(_dt(q)), _i(n), _i(n_heads), _i(1), _i(head_dim), _i(v_dim), _f(scale),
+            _p(sink), _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(cache.k), _p(cache.page_table),
+            _i(cache.table_width), _i(cache.tokens_per_page), _i(top), _p(parts), _ll(parts.numel()), _stream()),
+            "attention_split", kernels=2)
+        return
+    lib = load_module("attention_generic")
+    _check(lib, lib.abk_attention_values_in_keys(
+        _p(q), _ll(q.shape[1]), _p(out), _i(_dt(q)), _i(n), _i(n_heads), _i(1), _i(head_dim), _f(scale),
+        _p(batch.token_seq), _p(batch.token_pos), _p(batch.seq_slot), _p(batch.seq_start), _p(batch.seq_pos0), _p(cache.k),
+        _p(cache.page_table), _i(cache.table_width), _i(cache.tokens_per_page), _i(v_dim), _p(sink), _i(1), _stream()),
+        "attention")
+
+
+# ------------------------------------------------------------------ linear attention with a decay (csrc/lightning.cu)
+def lightning_scan(proj, q_at, k_at, v_at, n_heads, dim, vdim, decay, state, out, batch):
+    """Per head S <- decay_h S + k v^T, o = S^T q over every sequence of the step, token by token, from and into the
+    slots' states (float32 [slots, heads, dim, vdim]). q, k (heads x dim) and v (heads x vdim) are the SiLU of the
+    columns of proj from q_at, k_at and v_at on; out float32 [tokens, heads * vdim]."""
+    _need_cuda(proj, decay, state, out)
+    lib = load_module("lightning")
+    n_seqs = batch.seq_slot.numel()
+    assert proj.stride(1) == 1 and proj.shape[0] >= batch.n_rows and out.dtype == torch.float32 and out.is_contiguous()
+    assert out.shape[1] == n_heads * vdim and decay.dtype == torch.float32 and decay.numel() == n_heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, dim, vdim)
+    assert batch.seq_start.numel() >= n_seqs + 1
+    _check(lib, lib.abk_lightning_scan(_p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(q_at), _i(k_at), _i(v_at),
+                                       _i(n_heads), _i(dim), _i(vdim), _p(decay), _p(state), _p(out), _p(batch.seq_start),
+                                       _p(batch.seq_slot), _i(n_seqs), _stream()), "lightning_scan")
+
+
+def gated_row_norm(o, gate, weight, out, eps, batch):
+    """out[t] = weight * o[t] / sqrt(mean(o[t]^2) + eps) * sigmoid(gate[t]) over a token's whole row; o float32
+    [tokens, width], gate of out's type (rows of any pitch), weight float32 [width]; rows of padding become zeros."""
+    _need_cuda(o, gate, weight, out)
+    lib = load_module("lightning")
+    n, width = batch.n_rows, o.shape[1]
+    assert o.dtype == torch.float32 and o.is_contiguous() and out.is_contiguous() and out.shape[1] == width
+    assert gate.dtype == out.dtype and gate.stride(1) == 1 and gate.shape[1] >= width and weight.dtype == torch.float32
+    assert weight.numel() == width and o.shape[0] >= n and out.shape[0] >= n
+    _check(lib, lib.abk_gated_row_norm(_p(o), _p(gate), _ll(gate.stride(0)), _p(weight), _p(out), _i(_dt(out)), _i(n),
+                                       _i(width), _f(eps), _p(batch.token_seq), _stream()), "gated_row_norm")
+
+
+# ------------------------------------------------------------------ routed experts (csrc/moe.cu)
+RELU_SQUARED = 1
+
+
+def moe_route(x, router, top, batch, pair_expert, pair_weight, softmax_chosen=False):
+    """Per token the `top` experts with the largest router logits (router float32 [experts, d], x as stored) and their
+    weights, sigmoid(logit) or the softmax over the chosen; pair token * top + k is the token's k-th choice
+    (pair_expert int32, -1 for padding rows; pair_weight float32)."""
+    _need_cuda(x, router, pair_expert, pair_weight)
+    lib = load_module("moe")
+    n, (experts, d) = batch.n_rows, router.shape
+    assert router.dtype == torch.float32 and router.is_contiguous() and x.stride(1) == 1 and x.shape[1] == d
+    assert pair_expert.dtype == torch.int32 and pair_weight.dtype == torch.float32
+    assert pair_expert.numel() >= n * top and pair_weight.numel() >= n * top
+    _check(lib, lib.abk_moe_route(_p(x), _ll(x.stride(0)), _i(_dt(x)), _p(router), _i(n), _i(d), _i(experts), _i(top),
+                                  _i(1 if softmax_chosen else 0), _p(batch.token_seq), _p(pair_expert), _p(pair_weight),
+                                  _stream()), "moe_route")
+
+
+def routed_product(x, pairs_per_row, w, pair_expert, pair_scale, out, n_pairs, activation=0):
+    """out[p] = act(w[pair_expert[p]] (pair_scale[p] * x[p // pairs_per_row])) for p < n_pairs: a product whose matrix,
+    w [experts, outs, in], is chosen per row. pair_scale None: no scale; with one the scaled input is rounded to x's
+    type first. out of x's type or float32. activation: 0 none, RELU_SQUARED."""
+    _need_cuda(x, w, pair_expert, pair_scale, out)
+    lib = load_module("moe")
+    experts, outs, inner = w.shape
+    assert x.dtype == w.dtype and w.is_contiguous() and x.stride(1) == 1 and x.shape[1] == inner
+    assert out.stride(1) == 1 and out.shape[1] == outs and out.shape[0] >= n_pairs and out.dtype in (x.dtype, torch.float32)
+    _check(lib, lib.abk_routed_product(_p(x), _ll(x.stride(0)), _i(pairs_per_row), _i(_dt(x)), _p(w), _p(pair_expert),
+                                       _p(pair_scale), _p(out), _ll(out.stride(0)),
+                                       _i(1 if out.dtype == torch.float32 and x.dtype != torch.float32 else 0),
+                                       _i(activation), _i(n_pairs), _i(inner), _i(outs), _stream()), "routed_product")
+
+
+def moe_combine(pairs, out, n, top, add):
+    """out[t] = (out[t] if add else 0) + sum over k of pairs[t * top + k], in the order of k; all float32."""
+    _need_cuda(pairs, out)
+    lib = load_module("moe")
+    d = out.shape[1]
+    assert pairs.dtype == out.dtype == torch.float32 and pairs.is_contiguous() and out.is_contiguous()
+    assert pairs.shape[1] == d and pairs.shape[0] >= n * top and out.shape[0] >= n
+    _check(lib, lib.abk_moe_combine(_p(pairs), _p(out), _i(n), _i(d), _i(top), _i(1 if add else 0), _stream()), "moe_combine")
+
+
+def relu_squared(x, n):
+    """x[:n] = max(x, 0)^2 in place (x contiguous)."""
+    _need_cuda(x)
+    lib = load_module("moe")
+    assert x.is_contiguous()
+    _check(lib, lib.abk_relu_squared(_p(x), _i(_dt(x)), _ll(n * x.shape[1]), _stream()), "relu_squared")

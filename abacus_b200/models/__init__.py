@@ -1,4 +1,4 @@
-from . import qwen3, temetar  # noqa: F401  (register Qwen3ForCausalLM and Temetar)
+from . import movarax, qwen3, temetar  # noqa: F401  (register Qwen3ForCausalLM, Temetar and Movarax)
 from .layout import ModelLayout
 from .model import Model, expected_tensors
 

@@ -1,0 +1,77 @@
+"""A feed-forward of routed experts (config.specs.RoutedMLPSpec): a router picks `top` of `experts` small
+feed-forward layers for every token, an optional shared one runs for all.
+
+The router's logits, the scores and the choice are float32. A pair is (token, k-th choice); the experts' products run
+over pairs, each row against the matrices of its own expert (csrc/moe.cu), and a token's pairs are summed in the order
+of k, so a token's result does not depend on what else is in the step. The experts' matrices are kept stacked,
+[experts, out, in].
+"""
+import torch
+
+from ..kernels import ops
+from .base import FEED_FORWARDS, to_device
+from .linear import Linear
+
+_ACTIVATIONS = {"relu_squared": ops.RELU_SQUARED}
+
+
+@FEED_FORWARDS.register("routed_mlp")
+class RoutedMLP:
+    capturable = True  # its forward launches kernels only; the routing stays on the device
+
+    def __init__(self, spec):
+        s = self.spec = spec
+        if not 1 <= s.top <= s.experts:
+            raise ValueError(f"top {s.top} of {s.experts} experts")
+        if s.score not in ("sigmoid", "softmax_chosen"):
+            raise ValueError(f"router score {s.score!r} is neither sigmoid nor softmax_chosen")
+        if s.weight_on not in ("input", "output"):
+            raise ValueError(f"weight_on {s.weight_on!r} is neither input nor output")
+        for e in (s.expert, s.shared):
+            if e is not None and e.activation not in _ACTIVATIONS:
+                raise ValueError(f"expert activation {e.activation!r} is not built (only relu_squared)")
+
+    def param_shapes(self):
+        s = self.spec
+        shapes = {"router": (s.experts, s.hidden)}
+        for e in range(s.experts):
+            shapes[f"up{e}"] = (s.expert.inter, s.hidden)
+            shapes[f"down{e}"] = (s.hidden, s.expert.inter)
+        if s.shared is not None:
+            shapes.update(shared_up=(s.shared.inter, s.hidden), shared_down=(s.hidden, s.shared.inter))
+        return shapes
+
+    def bind(self, params, ctx):
+        s, self.ctx = self.spec, ctx
+        self.router = to_device(params["router"], ctx, torch.float32)
+        self.up = to_device(torch.stack([params[f"up{e}"] for e in range(s.experts)]), ctx, ctx.dtype)
+        self.down = to_device(torch.stack([params[f"down{e}"] for e in range(s.experts)]), ctx, ctx.dtype)
+        self.shared_up = self.shared_down = None
+        if s.shared is not None:
+            self.shared_up = Linear(to_device(params["shared_up"], ctx, ctx.dtype))
+            self.shared_down = Linear(to_device(params["shared_down"], ctx, ctx.dtype))
+
+    def step_weights(self):
+        # of the experts a step reads only those its tokens chose; the router and the shared expert it reads whole
+        shared = [self.shared_up.weight, self.shared_down.weight] if self.shared_up is not None else []
+        return [self.router, *shared]
+
+    def forward(self, xn, out, batch, ws):
+        s, n, dt = self.spec, batch.n_rows, self.ctx.dtype
+        pairs = n * s.top
+        expert = ws.get("moe_expert", (pairs,), torch.int32)
+        weight = ws.get("moe_weight", (pairs,), torch.float32)
+        ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen")
+        act = ws.get("moe_act", (pairs, s.expert.inter), dt)
+        on_input = s.weight_on == "input"
+        ops.routed_product(xn, s.top, self.up, expert, weight if on_input else None, act, pairs,
+                           activation=_ACTIVATIONS[s.expert.activation])
+        pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)
+        ops.routed_product(act, 1, self.down, expert, None if on_input else weight, pair_out, pairs)
+        if self.shared_up is not None:
+            shared_act = ws.get("moe_shared_act", (n, s.shared.inter), dt)
+            self.shared_up.forward(xn, shared_act, n)
+            ops.relu_squared(shared_act, n)
+            self.shared_down.forward(shared_act, out, n)
+        ops.moe_combine(pair_out, out, n, s.top, add=self.shared_up is not None)
+        return out

@@ -29,6 +29,13 @@ class Rotary:
         have = self._tables.get(key)
         if have is None or have[0].shape[0] < n_positions:
             half = self.rotary_dim // 2
+            if getattr(self.spec, "exact_angles", False):  # position * theta^(-2i / rotary_dim) in float64
+                i = np.arange(half, dtype=np.float64)
+                angle = np.arange(n_positions, dtype=np.float64)[:, None] * np.power(float(self.spec.theta), -2.0 * i / self.rotary_dim)[None, :]
+                have = (torch.from_numpy(np.cos(angle).astype(np.float32)).to(device),
+                        torch.from_numpy(np.sin(angle).astype(np.float32)).to(device))
+                self._tables[key] = have
+                return have
             i = np.arange(half, dtype=np.float32)
             inv = np.float32(1.0) / np.power(np.float32(self.spec.theta),
                                              (np.float32(2.0) * i) / np.float32(self.rotary_dim), dtype=np.float32)
