@@ -45,10 +45,7 @@ class MovaraxLatent:
         kv_from = m.get("kv_from")
         if kv_from is not None:
             kv_from = _int(where, m, "kv_from", 0)
-        dim = _int(where, m, "dim", 0)
-        if dim + rot_dim < 1:
-            raise ConfigError(f"config.json: {where}dim and rot_dim are both 0")
-        return cls(_int(where, m, "heads"), dim, rot_dim, _int(where, m, "vdim"), _int(where, m, "kv_rank"),
+        return cls(_int(where, m, "heads"), _int(where, m, "dim"), rot_dim, _int(where, m, "vdim"), _int(where, m, "kv_rank"),
                    _float(where, m, "scale"), base if dims else None, dims, kv_from)
 
     def to_dict(self):

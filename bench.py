@@ -443,6 +443,44 @@ def build_temetar(size):
     return model
 
 
+# Movarax at the same widths, depths and vocabulary: every fourth layer latent attention (heads of 128 + 64 rotated,
+# values of 128, 192 latents: a cache row of 256 elements a token for all heads; every second of them reads the latents
+# of the one before), the others linear attention with a decay per head (heads of 128 x 128 state); the first layer's
+# feed-forward dense, the others 16 experts of which a token uses 2, and a shared one, each a quarter of the dense size.
+MOVARAX_SIZES = {
+    "s": dict(heads=16, decay_heads=8, experts=16, top=2, expert_ff=768),
+    "m": dict(heads=32, decay_heads=20, experts=16, top=2, expert_ff=2432),
+}
+
+
+def build_movarax(size):
+    import torch
+    from abacus_b200.config import get_architecture
+    from abacus_b200.config.movarax import MovaraxConfig, MovaraxDecay, MovaraxDense, MovaraxExperts, MovaraxLatent, MovaraxLayer
+    from abacus_b200.models import Model
+    from abacus_b200.weights import random_tensors
+    z, v = DESIGN_SIZES[size], MOVARAX_SIZES[size]
+    layers = []
+    for i in range(z["layers"]):
+        mlp = MovaraxDense(z["ff"]) if i == 0 else MovaraxExperts(v["experts"], v["top"], v["expert_ff"], v["expert_ff"])
+        if i % 4 == 0:
+            mixer = MovaraxLatent(v["heads"], 128, 64, 128, 192, 192 ** -0.5, 1000000.0, 64, kv_from=i - 4 if i % 8 == 4 else None)
+            layers.append(MovaraxLayer("latent_attention", mixer, mlp))
+        else:
+            decay = tuple(1.0 - 2.0 ** -(3 + 5 * h / v["decay_heads"]) for h in range(v["decay_heads"]))
+            layers.append(MovaraxLayer("lightning", MovaraxDecay(v["decay_heads"], 128, 128, decay), mlp))
+    config = MovaraxConfig(vocab=z["vocab"], width=z["width"], layers=tuple(layers), eps=1e-6, embedding_scale=1.0)
+    arch = get_architecture("Movarax")
+    spec = config.to_spec()
+    expected, _ = arch.tensor_names(spec, None)
+    device = torch.device("cuda", 0)
+    tensors = random_tensors(expected, seed=5, std=0.02, device=device, rule=arch.random_moments)
+    model = Model(spec, arch.layout(spec), tensors, torch.bfloat16, device)
+    del tensors
+    torch.cuda.empty_cache()
+    return model
+
+
 def state_and_cache_bytes(model, tokens_held, n_seqs):
     """Bytes of keys, values and recurrent state a decode step moves for n_seqs sequences that hold tokens_held
     tokens together: a window's keys at most, a state read and written."""
@@ -454,7 +492,8 @@ def state_and_cache_bytes(model, tokens_held, n_seqs):
             per_seq = tokens_held / n_seqs
             if need.window is not None:
                 per_seq = min(per_seq, need.window + need.keep_first)
-            total += n_seqs * per_seq * need.n_kv_heads * (need.head_dim + (need.v_head_dim or need.head_dim)) * 2
+            values = 0 if need.values_in_keys else (need.v_head_dim or need.head_dim)  # (one pool: read once)
+            total += n_seqs * per_seq * need.n_kv_heads * (need.head_dim + values) * 2
         for _, shape, _ in need.states:
             count = 1
             for n in shape:
@@ -464,22 +503,28 @@ def state_and_cache_bytes(model, tokens_held, n_seqs):
 
 
 def run_design(args):
-    """--design temetar: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3 shape of equal size."""
+    """--design temetar | movarax: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3 shape of
+    equal size."""
     import torch
     from abacus_b200.kernels import build_all
     build_all(verbose=False)
     torch.cuda.set_device(0)
     pk = peaks()
     z = DESIGN_SIZES[args.size]
-    out = {"design": "Temetar", "size": args.size, "shape": {k: v for k, v in z.items() if k != "qwen"},
+    shape = {k: v for k, v in z.items() if k != "qwen"}
+    if args.design == "movarax":
+        shape = {**{k: shape[k] for k in ("width", "ff", "layers", "vocab")}, **MOVARAX_SIZES[args.size]}
+    out = {"design": args.design.capitalize(), "size": args.size, "shape": shape,
            "batch": args.batch, "prompt_tokens": PROMPT, "steps": args.steps, "warmup": args.warmup, "peaks": pk}
-    for which in ("temetar", "qwen3"):
+    for which in (args.design, "qwen3"):
         if which == "temetar":
             model = build_temetar(args.size)
+        elif which == "movarax":
+            model = build_movarax(args.size)
         else:
             model, _ = build_model(z["qwen"])
         prompts = prompts_for(args.batch, model.spec.vocab, 10 + args.batch)
-        run = device_decode(model, prompts, args.steps, args.warmup, CONTEXT, which == "temetar")
+        run = device_decode(model, prompts, args.steps, args.warmup, CONTEXT, which == args.design)
         bytes_step = model.weight_bytes_read_per_step() + state_and_cache_bytes(model, run["mean_tokens_held"], args.batch)
         one = prompts_for(1, model.spec.vocab, 99)[0][:PREFILL_TOKENS]
         pre_ms, _ = prefill(model, [one]) if which == "qwen3" else prefill_any(model, [one])
@@ -583,7 +628,7 @@ def main():
     ap.add_argument("--config", default="0.6b", choices=sorted(CONFIGS), help="whose workload the line reports")
     ap.add_argument("--skip-large", action="store_true", help="leave the 4b and 8b workloads out of `points`")
     ap.add_argument("--ragged", action="store_true", help="with --only prefill: the configuration's own prompts")
-    ap.add_argument("--design", default=None, choices=["temetar"],
+    ap.add_argument("--design", default=None, choices=["temetar", "movarax"],
                     help="instead of the default workload: this design at --size beside the Qwen3 shape of equal size")
     ap.add_argument("--size", default="s", choices=sorted(DESIGN_SIZES), help="with --design: the layer sizes")
     args = ap.parse_args()
