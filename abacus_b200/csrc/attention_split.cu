@@ -30,6 +30,7 @@ struct AttnSplit {
     PagedCache cache, v_cache;
     int n_parts;
     int values_in_keys;  // a value is the first v_dim elements of its key row (one pool)
+    int one_kv;          // the cache has one kv head; n_kv_heads counts runs of query heads that a CTA takes together
 };
 
 // (first key of the window, number of kept first keys before it, number of visible keys) of a token at pos
@@ -91,8 +92,9 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
     if (valid) {
         const int j = number < kept ? number : lo + number - kept;
         const int page = cache_page(p.cache, slot, j);
-        v_off[tid] = cache_offset(p.v_cache, page, kvh, p.n_kv_heads, j, p.values_in_keys ? hd : vd);
-        k_off[tid] = cache_offset(p.cache, page, kvh, p.n_kv_heads, j, hd);
+        const int ckv = p.one_kv ? 0 : kvh, cn = p.one_kv ? 1 : p.n_kv_heads;
+        v_off[tid] = cache_offset(p.v_cache, page, ckv, cn, j, p.values_in_keys ? hd : vd);
+        k_off[tid] = cache_offset(p.cache, page, ckv, cn, j, hd);
     }
     const T *q = (const T *)p.q + (long long)t * p.q_row + (long long)kvh * group * hd;
     for (int e = tid; e < group * hd; e += AS_THREADS) q_s[e] = to_float(q[e]);
@@ -233,6 +235,14 @@ static int attention_split(int values_in_keys, const void *q, long long q_row, v
     if (n_tokens <= 0) return 0;
     if (head_dim > AS_MAX_DIM || head_dim % 8 || head_dim < 8) ABK_REFUSE("attention_split: head_dim %d is not a multiple of 8 up to %d", head_dim, AS_MAX_DIM);
     if (v_dim < 1 || v_dim > AS_MAX_DIM) ABK_REFUSE("attention_split: value size %d is not 1 to %d", v_dim, AS_MAX_DIM);
+    int one_kv = 0;
+    if (values_in_keys && n_kv_heads == 1 && n_heads > AS_MAX_GROUP) {
+        // one kv head for more query heads than a CTA takes: the heads go in runs of the largest divisor up to 16,
+        // each run a CTA of its own over the same cache rows
+        int run = AS_MAX_GROUP;
+        while (n_heads % run) run--;
+        n_kv_heads = n_heads / run, one_kv = 1;
+    }
     if (n_kv_heads < 1 || n_heads % n_kv_heads || n_heads / n_kv_heads > AS_MAX_GROUP)
         ABK_REFUSE("attention_split: %d query heads to %d kv heads (groups of up to %d)", n_heads, n_kv_heads, AS_MAX_GROUP);
     if (n_heads > 65535 || max_keys < 1) ABK_REFUSE("attention_split: %d heads, %d keys", n_heads, max_keys);
@@ -245,7 +255,7 @@ static int attention_split(int values_in_keys, const void *q, long long q_row, v
     p.cache.tokens_per_page = tokens_per_page, p.cache.pinned_pages = pinned_pages;
     p.v_cache = p.cache;
     p.n_parts = (max_keys + AS_THREADS - 1) / AS_THREADS;
-    p.values_in_keys = values_in_keys;
+    p.values_in_keys = values_in_keys, p.one_kv = one_kv;
     if (values_in_keys && v_dim > head_dim) ABK_REFUSE("attention_split: values of %d inside keys of %d", v_dim, head_dim);
     if (p.n_parts > 65535) ABK_REFUSE("attention_split: %d keys are more than a grid takes", max_keys);
     if ((long long)n_tokens * n_heads * p.n_parts * (v_dim + 2) > parts_floats)

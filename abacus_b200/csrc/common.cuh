@@ -212,6 +212,52 @@ __device__ __forceinline__ float block_max(float v, float *scratch) {
     return scratch[32];
 }
 
+// A lane's share of w . x for a row of weights in global memory and x in shared memory (float32): 16-byte pieces of the
+// row where it allows (vec: the row starts on a 16-byte boundary and its length is a multiple of a piece), else an element at a
+// time. The lanes' shares are added by the caller (warp_sum). `rows` weight rows (1 to 4) `stride` elements apart against
+// the same x at once, so that their loads are in flight together.
+template <int ROWS> __device__ __forceinline__ void lane_dots(const float *w, long long stride, const float *x, int n, int lane,
+                                                              bool vec, float *acc) {
+    if (vec) {
+        for (int i = lane * 4; i < n; i += 128) {
+            float4 r[ROWS];
+#pragma unroll
+            for (int u = 0; u < ROWS; u++) r[u] = *(const float4 *)(w + u * stride + i);
+            const float4 a = *(const float4 *)(x + i);
+#pragma unroll
+            for (int u = 0; u < ROWS; u++)
+                acc[u] = fmaf(r[u].w, a.w, fmaf(r[u].z, a.z, fmaf(r[u].y, a.y, fmaf(r[u].x, a.x, acc[u]))));
+        }
+    } else {
+        for (int i = lane; i < n; i += 32)
+#pragma unroll
+            for (int u = 0; u < ROWS; u++) acc[u] = fmaf(w[u * stride + i], x[i], acc[u]);
+    }
+}
+template <int ROWS> __device__ __forceinline__ void lane_dots(const __nv_bfloat16 *w, long long stride, const float *x, int n,
+                                                              int lane, bool vec, float *acc) {
+    if (vec) {
+        for (int i = lane * 8; i < n; i += 256) {
+            uint4 r[ROWS];
+#pragma unroll
+            for (int u = 0; u < ROWS; u++) r[u] = *(const uint4 *)(w + u * stride + i);
+            const float4 a = *(const float4 *)(x + i), b = *(const float4 *)(x + i + 4);
+#pragma unroll
+            for (int u = 0; u < ROWS; u++) {
+                const __nv_bfloat162 *h = (const __nv_bfloat162 *)&r[u];
+                const float2 f0 = __bfloat1622float2(h[0]), f1 = __bfloat1622float2(h[1]), f2 = __bfloat1622float2(h[2]),
+                             f3 = __bfloat1622float2(h[3]);
+                acc[u] = fmaf(f1.y, a.w, fmaf(f1.x, a.z, fmaf(f0.y, a.y, fmaf(f0.x, a.x, acc[u]))));
+                acc[u] = fmaf(f3.y, b.w, fmaf(f3.x, b.z, fmaf(f2.y, b.y, fmaf(f2.x, b.x, acc[u]))));
+            }
+        }
+    } else {
+        for (int i = lane; i < n; i += 32)
+#pragma unroll
+            for (int u = 0; u < ROWS; u++) acc[u] = fmaf(__bfloat162float(w[u * stride + i]), x[i], acc[u]);
+    }
+}
+
 // Where a position of a sequence lies in a paged cache.
 //   tokens_per_page keys per page; a sequence's pages are listed in its row of the page table.
 //   ring_pages > 0: the sequence keeps only that many pages and position p lives in

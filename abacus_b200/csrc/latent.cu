@@ -121,31 +121,27 @@ template <typename T>
 __global__ void __launch_bounds__(128) head_product_kernel(const T *__restrict__ x, long long ldx, int x_head,
                                                            const T *__restrict__ w, T *__restrict__ out, long long ldo,
                                                            int o_head, int n, int in, int outs) {
-    extern __shared__ float hp_x[];  // [HP_ROWS][in]
+    extern __shared__ __align__(16) float hp_x[];  // [HP_ROWS][in4], in4 = in rounded up to 4
     const int h = blockIdx.y, r0 = blockIdx.z * HP_ROWS, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int rows = n - r0 < HP_ROWS ? n - r0 : HP_ROWS;
     pdl_wait();
+    const int in4 = (in + 3) & ~3;
     for (int e = threadIdx.x; e < HP_ROWS * in; e += 128) {
         const int r = e / in, i = e - r * in;
-        hp_x[e] = r < rows ? to_float(x[(long long)(r0 + r) * ldx + (long long)h * x_head + i]) : 0.0f;
+        hp_x[r * in4 + i] = r < rows ? to_float(x[(long long)(r0 + r) * ldx + (long long)h * x_head + i]) : 0.0f;
     }
     __syncthreads();
+    const bool vec = in % (16 / (int)sizeof(T)) == 0 && ((uintptr_t)w & 15) == 0;
     for (int u = 0; u < HP_PER_WARP; u++) {
         const int o = (blockIdx.x * 4 + warp) * HP_PER_WARP + u;
         if (o >= outs) break;
         const T *wr = w + ((long long)h * outs + o) * in;
-        float acc[HP_ROWS];
-#pragma unroll
-        for (int r = 0; r < HP_ROWS; r++) acc[r] = 0.0f;
-        for (int i = lane; i < in; i += 32) {
-            const float wv = to_float(wr[i]);
-#pragma unroll
-            for (int r = 0; r < HP_ROWS; r++) acc[r] = fmaf(wv, hp_x[r * in + i], acc[r]);
-        }
-#pragma unroll
-        for (int r = 0; r < HP_ROWS; r++) {
-            const float v = warp_sum(acc[r]);
-            if (lane == 0 && r < rows) out[(long long)(r0 + r) * ldo + (long long)h * o_head + o] = from_float<T>(v);
+        // a row of the matrix against each of the CTA's rows of x: the lanes' shares of the sums, each in its own order
+        for (int r = 0; r < rows; r++) {
+            float acc = 0.0f;
+            lane_dots<1>(wr, 0, hp_x + r * in4, in, lane, vec, &acc);
+            acc = warp_sum(acc);
+            if (lane == 0) out[(long long)(r0 + r) * ldo + (long long)h * o_head + o] = from_float<T>(acc);
         }
     }
 }
@@ -159,7 +155,7 @@ extern "C" int abk_head_product(const void *x, long long ldx, int x_head, const 
     const long long row_tiles = ((long long)n + HP_ROWS - 1) / HP_ROWS;
     if (heads > 65535 || row_tiles > 65535) ABK_REFUSE("head_product: %d heads, %d rows are more than a grid takes", heads, n);
     dim3 grid((outs + 4 * HP_PER_WARP - 1) / (4 * HP_PER_WARP), heads, (unsigned)row_tiles);
-    const size_t smem = (size_t)HP_ROWS * in * sizeof(float);
+    const size_t smem = (size_t)HP_ROWS * ((in + 3) & ~3) * sizeof(float);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16) {
         if (smem > 48 * 1024) {

@@ -15,26 +15,27 @@
 #define ABK_DEFINE_ERROR
 #include "common.cuh"
 
+#define MR_THREADS 256
 template <typename T>
-__global__ void __launch_bounds__(128) moe_route_kernel(const T *x, long long ldx, const float *router, int d, int experts,
+__global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T *x, long long ldx, const float *router, int d, int experts,
                                                         int top, int softmax_chosen, const int *token_seq, int *pair_expert,
                                                         float *pair_weight) {
-    extern __shared__ float mr_smem[];  // [d] the row, [experts] logits, [experts] taken flags
-    float *xs = mr_smem, *z = xs + d;
+    extern __shared__ __align__(16) float mr_smem[];  // [d, rounded up to 4] the row, [experts] logits, [experts] taken flags
+    float *xs = mr_smem, *z = xs + ((d + 3) & ~3);
     int *taken = (int *)(z + experts);
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     pdl_wait();
     if (token_seq[t] < 0) {
-        for (int k = tid; k < top; k += 128) pair_expert[(long long)t * top + k] = -1, pair_weight[(long long)t * top + k] = 0.0f;
+        for (int k = tid; k < top; k += MR_THREADS) pair_expert[(long long)t * top + k] = -1, pair_weight[(long long)t * top + k] = 0.0f;
         return;
     }
-    for (int i = tid; i < d; i += 128) xs[i] = to_float(x[(long long)t * ldx + i]);
-    for (int e = tid; e < experts; e += 128) taken[e] = 0;
+    for (int i = tid; i < d; i += MR_THREADS) xs[i] = to_float(x[(long long)t * ldx + i]);
+    for (int e = tid; e < experts; e += MR_THREADS) taken[e] = 0;
     __syncthreads();
-    for (int e = warp; e < experts; e += 4) {
-        const float *r = router + (long long)e * d;
+    const bool vec = d % 4 == 0 && ((uintptr_t)router & 15) == 0;
+    for (int e = warp; e < experts; e += MR_THREADS / 32) {
         float acc = 0.0f;
-        for (int i = lane; i < d; i += 32) acc = fmaf(r[i], xs[i], acc);
+        lane_dots<1>(router + (long long)e * d, 0, xs, d, lane, vec, &acc);
         acc = warp_sum(acc);
         if (lane == 0) z[e] = acc;
     }
@@ -73,7 +74,7 @@ extern "C" int abk_moe_route(const void *x, long long ldx, int dtype, const floa
                              void *stream) {
     if (n_tokens <= 0) return 0;
     if (top < 1 || top > experts) ABK_REFUSE("moe_route: %d of %d experts", top, experts);
-    const size_t smem = (size_t)(d + 2 * experts) * 4;
+    const size_t smem = (size_t)(((d + 3) & ~3) + 2 * experts) * 4;
     if (smem > 200 * 1024) ABK_REFUSE("moe_route: a row of %d and %d experts do not fit shared memory", d, experts);
     cudaStream_t s = (cudaStream_t)stream;
     if (dtype == ABK_BF16) {
@@ -81,14 +82,14 @@ extern "C" int abk_moe_route(const void *x, long long ldx, int dtype, const floa
             cudaError_t e = abk_allow_shared_memory((const void *)moe_route_kernel<__nv_bfloat16>, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        abk_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(128), smem, s, (const __nv_bfloat16 *)x, ldx, router,
+        abk_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(MR_THREADS), smem, s, (const __nv_bfloat16 *)x, ldx, router,
                    d, experts, top, softmax_chosen, token_seq, pair_expert, pair_weight);
     } else {
         if (smem > 48 * 1024) {
             cudaError_t e = abk_allow_shared_memory((const void *)moe_route_kernel<float>, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
-        abk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(128), smem, s, (const float *)x, ldx, router, d, experts, top,
+        abk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(MR_THREADS), smem, s, (const float *)x, ldx, router, d, experts, top,
                    softmax_chosen, token_seq, pair_expert, pair_weight);
     }
     return ABK_LAUNCH_RESULT();
@@ -102,7 +103,7 @@ __global__ void __launch_bounds__(128) routed_product_kernel(const T *__restrict
                                                              const T *__restrict__ w, const int *pair_expert,
                                                              const float *pair_scale, TO *__restrict__ out, long long ldo,
                                                              int in, int outs) {
-    extern __shared__ float rp_x[];  // [in]
+    extern __shared__ __align__(16) float rp_x[];  // [in]
     const int pair = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     pdl_wait();
     const int e = pair_expert[pair];
@@ -119,15 +120,18 @@ __global__ void __launch_bounds__(128) routed_product_kernel(const T *__restrict
         for (int i = threadIdx.x; i < in; i += 128) rp_x[i] = to_float(row[i]);
     }
     __syncthreads();
+    if (o0 >= outs) return;
+    const T *wr = w + ((long long)e * outs + o0) * in;
+    const bool vec = in % (16 / (int)sizeof(T)) == 0 && ((uintptr_t)w & 15) == 0;
+    float acc[RP_PER_WARP] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (o0 + RP_PER_WARP <= outs) lane_dots<RP_PER_WARP>(wr, in, rp_x, in, lane, vec, acc);  // four rows' loads in flight together
+    else
+        for (int u = 0; o0 + u < outs; u++) lane_dots<1>(wr + (long long)u * in, 0, rp_x, in, lane, vec, acc + u);
+#pragma unroll
     for (int u = 0; u < RP_PER_WARP; u++) {
-        const int o = o0 + u;
-        if (o >= outs) break;
-        const T *wr = w + ((long long)e * outs + o) * in;
-        float acc = 0.0f;
-        for (int i = lane; i < in; i += 32) acc = fmaf(to_float(wr[i]), rp_x[i], acc);
-        acc = warp_sum(acc);
-        if (ACT == RP_RELU_SQUARED) acc = acc > 0.0f ? acc * acc : 0.0f;
-        if (lane == 0) out[(long long)pair * ldo + o] = from_float<TO>(acc);
+        float v = warp_sum(acc[u]);
+        if (ACT == RP_RELU_SQUARED) v = v > 0.0f ? v * v : 0.0f;
+        if (lane == 0 && o0 + u < outs) out[(long long)pair * ldo + o0 + u] = from_float<TO>(v);
     }
 }
 

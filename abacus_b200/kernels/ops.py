@@ -908,7 +908,7 @@ def spread_shared(shared, keys, k_head, at, count, heads, n):
 def attention_values_in_keys(q, out, n_heads, head_dim, v_dim, scale, batch, cache, sink=None, ws=None):
     """Causal attention of every token of the step over a cache with one kv head whose values are the first v_dim
     elements of its keys (latent rows), float32 softmax weights, an optional sink. q [tokens, n_heads * head_dim], out
-    [tokens, n_heads * v_dim]. A step of one token a sequence in bfloat16 with up to 16 heads and rows of up to 256
+    [tokens, n_heads * v_dim]. A step of one token a sequence in bfloat16 with rows of up to 256
     runs split along the keys (csrc/attention_split.cu), everything else on the general kernel."""
     _need_cuda(q, out, sink)
     n = batch.n_rows
@@ -916,8 +916,7 @@ def attention_values_in_keys(q, out, n_heads, head_dim, v_dim, scale, batch, cac
     assert out.shape[1] == n_heads * v_dim and cache.k.dtype == q.dtype and cache.k.shape[1:] == (1, cache.tokens_per_page, head_dim)
     assert cache.values_in_keys and cache.ring_pages == 0 and v_dim <= head_dim
     assert sink is None or (sink.dtype == torch.float32 and sink.numel() == n_heads)
-    if (batch.is_decode and ws is not None and q.dtype == torch.bfloat16 and n_heads <= 16 and head_dim % 8 == 0
-            and head_dim <= 256):
+    if batch.is_decode and ws is not None and q.dtype == torch.bfloat16 and head_dim % 8 == 0 and head_dim <= 256:
         lib = load_module("attention_split")
         top = getattr(batch, "position_bound", None) or batch.max_len_after
         if batch.max_len_after > top:
@@ -1018,3 +1017,61 @@ def relu_squared(x, n):
     lib = load_module("moe")
     assert x.is_contiguous()
     _check(lib, lib.abk_relu_squared(_p(x), _i(_dt(x)), _ll(n * x.shape[1]), _stream()), "relu_squared")
+
+
+# ------------------------------------------------------------------ routed experts over many rows (csrc/gemm_grouped.cu)
+GROUPED_ROWS = 128  # rows of a tile of the grouped product: an expert's run of sorted rows is padded to whole tiles
+
+
+def grouped_tiles(n_pairs, experts):
+    """Row tiles that hold n_pairs pairs sorted by expert, whatever the routing."""
+    return -(-n_pairs // GROUPED_ROWS) + experts
+
+
+def grouped_takes(x, up, down):
+    """Whether the tensor-core products by expert take these: bfloat16, inner sizes multiples of 8, 16-byte aligned."""
+    return (x.dtype == torch.bfloat16 and up.dtype == torch.bfloat16 and up.shape[2] % 8 == 0 and down.shape[2] % 8 == 0
+            and up.data_ptr() % 16 == 0 and down.data_ptr() % 16 == 0)
+
+
+def moe_sort(x, pairs_per_row, pair_expert, pair_scale, n_pairs, experts, scratch, place, tile_expert, sorted_rows):
+    """Pairs sorted by expert, each expert's run padded to whole tiles of 128 rows: place[p] int32 is pair p's row in
+    the sorted order (-1 for pairs of padding rows), tile_expert[t] int32 the expert of row tile t (-1 beyond the used
+    ones), sorted_rows bfloat16 [tiles * 128, d] the pairs' input rows x[p // pairs_per_row], times pair_scale[p]
+    where given. scratch int32 [2 * experts + n_pairs]."""
+    _need_cuda(x, pair_expert, pair_scale, scratch, place, tile_expert, sorted_rows)
+    lib = load_module("gemm_grouped")
+    d, max_tiles = x.shape[1], tile_expert.numel()
+    assert x.dtype == torch.bfloat16 and x.stride(1) == 1 and sorted_rows.dtype == torch.bfloat16 and sorted_rows.is_contiguous()
+    assert sorted_rows.shape == (max_tiles * GROUPED_ROWS, d) and scratch.dtype == torch.int32 and scratch.numel() >= 2 * experts + n_pairs
+    assert place.dtype == torch.int32 and place.numel() >= n_pairs and tile_expert.dtype == torch.int32
+    counts, first, rank = scratch[:experts], scratch[experts:2 * experts], scratch[2 * experts:]
+    _check(lib, lib.abk_moe_sort(_p(x), _ll(x.stride(0)), _i(pairs_per_row), _p(pair_expert), _p(pair_scale), _i(n_pairs),
+                                 _i(experts), _i(d), _p(counts), _p(rank), _p(first), _p(place), _p(tile_expert),
+                                 _i(max_tiles), _p(sorted_rows), _stream()), "moe_sort", kernels=3)
+
+
+def gemm_grouped(x, w, out, tile_expert, activation=0):
+    """out[p] = act(w[tile_expert[p // 128]] x[p]) for the sorted rows x bfloat16 [tiles * 128, K] on the tcgen05 tensor
+    cores; w bfloat16 [experts, N, K]; out bfloat16 or float32 [tiles * 128, N]. Tiles whose expert is -1 are left alone."""
+    _need_cuda(x, w, out, tile_expert)
+    lib = load_module("gemm_grouped")
+    experts, n, k = w.shape
+    tiles = tile_expert.numel()
+    assert x.dtype == torch.bfloat16 and w.dtype == torch.bfloat16 and x.is_contiguous() and w.is_contiguous()
+    assert x.shape == (tiles * GROUPED_ROWS, k) and out.shape == (tiles * GROUPED_ROWS, n) and out.stride(1) == 1
+    assert out.dtype in (torch.bfloat16, torch.float32)
+    _check(lib, lib.abk_gemm_grouped(_p(x), _p(w), _p(out), _ll(out.stride(0)), _i(1 if out.dtype == torch.float32 else 0),
+                                     _i(activation), _i(tiles), _i(experts), _i(n), _i(k), _p(tile_expert),
+                                     _p(kernel_status(x.device)), _stream()), "gemm_grouped")
+
+
+def moe_unsort(sorted_out, place, out, n, top, add):
+    """out[t] = (out[t] if add else 0) + sum over k of sorted_out[place[t * top + k]], in the order of k; float32."""
+    _need_cuda(sorted_out, place, out)
+    lib = load_module("gemm_grouped")
+    d = out.shape[1]
+    assert sorted_out.dtype == out.dtype == torch.float32 and sorted_out.is_contiguous() and out.is_contiguous()
+    assert sorted_out.shape[1] == d and place.dtype == torch.int32 and place.numel() >= n * top and out.shape[0] >= n
+    _check(lib, lib.abk_moe_unsort(_p(sorted_out), _p(place), _p(out), _i(n), _i(d), _i(top), _i(1 if add else 0), _stream()),
+           "moe_unsort")

@@ -2,9 +2,11 @@
 feed-forward layers for every token, an optional shared one runs for all.
 
 The router's logits, the scores and the choice are float32. A pair is (token, k-th choice); the experts' products run
-over pairs, each row against the matrices of its own expert (csrc/moe.cu), and a token's pairs are summed in the order
-of k, so a token's result does not depend on what else is in the step. The experts' matrices are kept stacked,
-[experts, out, in].
+over pairs, and a token's pairs are summed in the order of k, so a token's result does not depend on what else is in
+the step. The experts' matrices are kept stacked, [experts, out, in]. A handful of pairs (a decode step) runs each row
+against the matrices of its own expert as they stream from memory (csrc/moe.cu); more than GROUPED_FROM pairs in
+bfloat16 are sorted by expert, each expert's run padded to whole row tiles, and multiplied on the tensor cores
+(csrc/gemm_grouped.cu).
 """
 import torch
 
@@ -13,6 +15,9 @@ from .base import FEED_FORWARDS, to_device
 from .linear import Linear
 
 _ACTIVATIONS = {"relu_squared": ops.RELU_SQUARED}
+# From how many pairs on the rows are sorted by expert for the tensor cores: below, a pair's expert streams once for
+# its one row, which is what a tile of 128 rows with one row in it would do with more set-up.
+GROUPED_FROM = 64
 
 
 @FEED_FORWARDS.register("routed_mlp")
@@ -62,16 +67,30 @@ class RoutedMLP:
         expert = ws.get("moe_expert", (pairs,), torch.int32)
         weight = ws.get("moe_weight", (pairs,), torch.float32)
         ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen")
-        act = ws.get("moe_act", (pairs, s.expert.inter), dt)
         on_input = s.weight_on == "input"
-        ops.routed_product(xn, s.top, self.up, expert, weight if on_input else None, act, pairs,
-                           activation=_ACTIVATIONS[s.expert.activation])
-        pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)
-        ops.routed_product(act, 1, self.down, expert, None if on_input else weight, pair_out, pairs)
         if self.shared_up is not None:
             shared_act = ws.get("moe_shared_act", (n, s.shared.inter), dt)
             self.shared_up.forward(xn, shared_act, n)
             ops.relu_squared(shared_act, n)
             self.shared_down.forward(shared_act, out, n)
+        if pairs > GROUPED_FROM and on_input and ops.grouped_takes(xn, self.up, self.down):
+            tiles = ops.grouped_tiles(pairs, s.experts)
+            rows = tiles * ops.GROUPED_ROWS
+            scratch = ws.get("moe_sort", (2 * s.experts + pairs,), torch.int32)
+            place = ws.get("moe_place", (pairs,), torch.int32)
+            tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
+            sorted_rows = ws.get("moe_sorted", (rows, s.hidden), dt)
+            ops.moe_sort(xn, s.top, expert, weight, pairs, s.experts, scratch, place, tile_expert, sorted_rows)
+            act = ws.get("moe_act", (rows, s.expert.inter), dt)
+            ops.gemm_grouped(sorted_rows, self.up, act, tile_expert, activation=_ACTIVATIONS[s.expert.activation])
+            sorted_out = ws.get("moe_pair_out", (rows, s.hidden), torch.float32)
+            ops.gemm_grouped(act, self.down, sorted_out, tile_expert)
+            ops.moe_unsort(sorted_out, place, out, n, s.top, add=self.shared_up is not None)
+            return out
+        act = ws.get("moe_act", (pairs, s.expert.inter), dt)
+        ops.routed_product(xn, s.top, self.up, expert, weight if on_input else None, act, pairs,
+                           activation=_ACTIVATIONS[s.expert.activation])
+        pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)
+        ops.routed_product(act, 1, self.down, expert, None if on_input else weight, pair_out, pairs)
         ops.moe_combine(pair_out, out, n, s.top, add=self.shared_up is not None)
         return out

@@ -502,6 +502,20 @@ def state_and_cache_bytes(model, tokens_held, n_seqs):
     return total
 
 
+def routed_expert_bytes(model, n_rows):
+    """Bytes of routed experts' matrices a step of n_rows tokens reads: the experts its tokens choose, each once. With
+    random weights the choice is near uniform: experts x (1 - (1 - 1/experts)^(rows x top)) distinct experts on average."""
+    total = 0.0
+    for e in model.schedule:
+        ffn = getattr(model.blocks[e.layer], "ffn", None) if getattr(model.blocks[e.layer], "has_ffn", True) else None
+        spec = getattr(ffn, "spec", None)
+        if spec is None or getattr(spec, "kind", "") != "routed_mlp":
+            continue
+        distinct = spec.experts * (1.0 - (1.0 - 1.0 / spec.experts) ** (n_rows * spec.top))
+        total += distinct * 2 * spec.hidden * spec.expert.inter * ffn.up.element_size()
+    return total
+
+
 def run_design(args):
     """--design temetar | movarax: decode and prefill of the design at DESIGN_SIZES[--size] beside the Qwen3 shape of
     equal size."""
@@ -525,7 +539,8 @@ def run_design(args):
             model, _ = build_model(z["qwen"])
         prompts = prompts_for(args.batch, model.spec.vocab, 10 + args.batch)
         run = device_decode(model, prompts, args.steps, args.warmup, CONTEXT, which == args.design)
-        bytes_step = model.weight_bytes_read_per_step() + state_and_cache_bytes(model, run["mean_tokens_held"], args.batch)
+        bytes_step = (model.weight_bytes_read_per_step() + state_and_cache_bytes(model, run["mean_tokens_held"], args.batch)
+                      + routed_expert_bytes(model, args.batch))
         one = prompts_for(1, model.spec.vocab, 99)[0][:PREFILL_TOKENS]
         pre_ms, _ = prefill(model, [one]) if which == "qwen3" else prefill_any(model, [one])
         out[which] = {"decode_tok_s": round(run["tok_s"], 1), "decode_ms_per_step": round(run["ms_step"], 4),

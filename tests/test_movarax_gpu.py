@@ -249,6 +249,25 @@ def test_the_router_and_the_products_by_expert(dtype, E, top, d, ff):
     np.testing.assert_allclose(host(out), want, **(dict(rtol=2e-5, atol=2e-5) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)))
     ops.moe_combine(pair_out, out, T, top, add=False)
     np.testing.assert_allclose(host(out), want - 1.0, **(dict(rtol=2e-5, atol=2e-5) if dtype == "float32" else dict(rtol=2e-2, atol=2e-2)))
+    if ops.grouped_takes(x, up, down):
+        # the same over rows sorted by expert, on the tensor cores: an expert's run of rows padded to whole tiles
+        tiles = ops.grouped_tiles(T * top, E)
+        scratch = torch.empty(2 * E + T * top, dtype=torch.int32, device=DEV)
+        place, tile_expert = torch.empty(T * top, dtype=torch.int32, device=DEV), torch.empty(tiles, dtype=torch.int32, device=DEV)
+        rows = torch.full((tiles * 128, d), float("nan"), dtype=DT[dtype], device=DEV)   # (padding rows hold anything)
+        ops.moe_sort(x, top, expert, weight, T * top, E, scratch, place, tile_expert, rows)
+        places = place.cpu().numpy()
+        assert len(set(places.tolist())) == T * top and (tile_expert.cpu().numpy()[places // 128] == chosen.reshape(-1)).all()
+        act2 = torch.empty((tiles * 128, ff), dtype=DT[dtype], device=DEV)
+        ops.gemm_grouped(rows, up, act2, tile_expert, activation=ops.RELU_SQUARED)
+        sorted_out = torch.empty((tiles * 128, d), dtype=torch.float32, device=DEV)
+        ops.gemm_grouped(act2, down, sorted_out, tile_expert)
+        out2 = dev(np.ones((T, d)))
+        ops.moe_unsort(sorted_out, place, out2, T, top, add=True)
+        np.testing.assert_allclose(host(out2), want, rtol=2e-2, atol=2e-2)
+        ops.moe_unsort(sorted_out, place, out2, T, top, add=False)
+        np.testing.assert_allclose(host(out2), want - 1.0, rtol=2e-2, atol=2e-2)
+        assert not ops.kernel_status(x.device).any()
     sq = dev(h, DT[dtype])
     ops.relu_squared(sq, T)
     np.testing.assert_allclose(host(sq), rnd(plain.relu_squared(h)), rtol=1e-6, atol=1e-6)
