@@ -68,7 +68,27 @@ template <> __device__ __forceinline__ float dot_q<__nv_bfloat16>(const float *q
 // reading its own row meets no bank conflict), and once the scores are made the 128 value rows into the same memory,
 // under the softmax; else each thread reads global memory.
 // GMAX: the group's size rounded up to 1, 2, 4, 8 or 16 (what the loops over its heads are unrolled to).
-template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(AS_THREADS) attention_split_kernel(AttnSplit p) {
+__device__ __forceinline__ void as_mma_bf16(float *c, uint32_t a0, uint32_t a1, uint32_t a2, uint32_t a3, uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0, %1, %2, %3}, {%4, %5, %6, %7}, {%8, %9}, {%0, %1, %2, %3};"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3]) : "r"(a0), "r"(a1), "r"(a2), "r"(a3), "r"(b0), "r"(b1));
+}
+// A float32 number as three bfloat16 numbers that add up to it (its 24 bits), each pair packed for one operand register.
+__device__ __forceinline__ void as_split3(float x, float y, uint32_t &hi, uint32_t &mid, uint32_t &lo) {
+    const __nv_bfloat16 xh = __float2bfloat16_rn(x), yh = __float2bfloat16_rn(y);
+    const float xr = x - __bfloat162float(xh), yr = y - __bfloat162float(yh);
+    const __nv_bfloat16 xm = __float2bfloat16_rn(xr), ym = __float2bfloat16_rn(yr);
+    const __nv_bfloat16 xl = __float2bfloat16_rn(xr - __bfloat162float(xm)), yl = __float2bfloat16_rn(yr - __bfloat162float(ym));
+    hi = (uint32_t)__bfloat16_as_ushort(xh) | ((uint32_t)__bfloat16_as_ushort(yh) << 16);
+    mid = (uint32_t)__bfloat16_as_ushort(xm) | ((uint32_t)__bfloat16_as_ushort(ym) << 16);
+    lo = (uint32_t)__bfloat16_as_ushort(xl) | ((uint32_t)__bfloat16_as_ushort(yl) << 16);
+}
+
+// TC (bfloat16, STAGED, keys that carry their values, head_dim a multiple of 16, values a multiple of 8 up to 256): both
+// products on the warp-level tensor cores, the group's heads as the 16 rows of a tile. Scores: q from global memory
+// as the row operand, the staged key rows as the column operand, float32 sums. Weighted values: the float32 weights
+// as three bfloat16 parts that hold their 24 bits, each multiplied with the same value fragment, so that the weights
+// stay float32 in effect.
+template <typename T, bool STAGED, int GMAX, bool TC = false> __global__ void __launch_bounds__(AS_THREADS) attention_split_kernel(AttnSplit p) {
     extern __shared__ __align__(16) float as_smem[];
     const int group = p.n_heads / p.n_kv_heads, hd = p.head_dim, vd = p.v_dim;
     float *q_s = as_smem;                      // [group][hd]
@@ -112,7 +132,36 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
         __syncthreads();
     }
     float sc[GMAX];
-    if (valid) {
+    if (TC) {
+        const int row = lane >> 2, k0 = (lane & 3) * 2;
+        const __nv_bfloat16 *qg = (const __nv_bfloat16 *)p.q + (long long)t * p.q_row + (long long)kvh * group * hd;
+        const bool lower = row < group, upper = row + 8 < group;
+        float acc[4][4];
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) acc[nt][0] = acc[nt][1] = acc[nt][2] = acc[nt][3] = 0.0f;
+        for (int kk = 0; kk < hd; kk += 16) {
+            const uint32_t a0 = lower ? *(const uint32_t *)(qg + (long long)row * hd + kk + k0) : 0u;
+            const uint32_t a1 = upper ? *(const uint32_t *)(qg + (long long)(row + 8) * hd + kk + k0) : 0u;
+            const uint32_t a2 = lower ? *(const uint32_t *)(qg + (long long)row * hd + kk + k0 + 8) : 0u;
+            const uint32_t a3 = upper ? *(const uint32_t *)(qg + (long long)(row + 8) * hd + kk + k0 + 8) : 0u;
+#pragma unroll
+            for (int nt = 0; nt < 4; nt++) {
+                const uint8_t *kr = k_s + (warp * 32 + nt * 8 + row) * k_pitch + (kk + k0) * 2;
+                as_mma_bf16(acc[nt], a0, a1, a2, a3, *(const uint32_t *)kr, *(const uint32_t *)(kr + 16));
+            }
+        }
+        // the scores to where the weights will stand, [head][key]; every thread then takes its own key's
+#pragma unroll
+        for (int nt = 0; nt < 4; nt++) {
+            const int key = warp * 32 + nt * 8 + k0;
+            if (lower) p_s[row * AS_THREADS + key] = acc[nt][0] * p.scale, p_s[row * AS_THREADS + key + 1] = acc[nt][1] * p.scale;
+            if (upper) p_s[(row + 8) * AS_THREADS + key] = acc[nt][2] * p.scale, p_s[(row + 8) * AS_THREADS + key + 1] = acc[nt][3] * p.scale;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int g = 0; g < GMAX; g++)
+            if (g < group) sc[g] = valid ? p_s[g * AS_THREADS + tid] : -INFINITY;
+    } else if (valid) {
         const T *k = STAGED ? (const T *)(k_s + tid * k_pitch) : (const T *)p.k_pool + k_off[tid];
 #pragma unroll
         for (int g = 0; g < GMAX; g++)
@@ -159,6 +208,62 @@ template <typename T, bool STAGED, int GMAX> __global__ void __launch_bounds__(A
     }
     if (STAGED && !p.values_in_keys) asm volatile("cp.async.wait_group 0;" ::: "memory");  // the values are here
     __syncthreads();
+    if (TC) {
+        // out[head][column] = sum over the part's keys of weight[head][key] * value[key][column]: a warp has every fourth
+        // tile of 8 columns; a key step's weights are split once and meet all of the warp's tiles
+        const int row = lane >> 2, k0 = (lane & 3) * 2;
+        const bool lower = row < group, upper = row + 8 < group;
+        const int n_tiles = vd / 8;
+        float c[8][4];
+#pragma unroll
+        for (int i = 0; i < 8; i++) c[i][0] = c[i][1] = c[i][2] = c[i][3] = 0.0f;
+        for (int ks = 0; ks < AS_THREADS; ks += 16) {
+            if (ks >= n_valid) break;
+            uint32_t ah[4], am[4], al[4];
+            const float *pl = p_s + row * AS_THREADS + ks + k0, *pu = p_s + (row + 8) * AS_THREADS + ks + k0;
+            as_split3(lower ? pl[0] : 0.0f, lower ? pl[1] : 0.0f, ah[0], am[0], al[0]);
+            as_split3(upper ? pu[0] : 0.0f, upper ? pu[1] : 0.0f, ah[1], am[1], al[1]);
+            as_split3(lower ? pl[8] : 0.0f, lower ? pl[9] : 0.0f, ah[2], am[2], al[2]);
+            as_split3(upper ? pu[8] : 0.0f, upper ? pu[9] : 0.0f, ah[3], am[3], al[3]);
+            // keys beyond the part's last hold whatever the memory held: their values are taken as zeros
+            const bool in0 = ks + k0 < n_valid, in1 = ks + k0 + 1 < n_valid, in8 = ks + k0 + 8 < n_valid, in9 = ks + k0 + 9 < n_valid;
+            const uint8_t *vr = k_s + (ks + k0) * k_pitch + row * 2;
+#pragma unroll
+            for (int i = 0; i < 8; i++) {
+                const int nt = warp + 4 * i;
+                if (nt >= n_tiles) break;
+                const uint8_t *v = vr + nt * 16;
+                const uint32_t v0 = in0 ? *(const uint16_t *)v : 0u, v1 = in1 ? *(const uint16_t *)(v + k_pitch) : 0u;
+                const uint32_t v8 = in8 ? *(const uint16_t *)(v + 8 * k_pitch) : 0u, v9 = in9 ? *(const uint16_t *)(v + 9 * k_pitch) : 0u;
+                const uint32_t b0 = v0 | (v1 << 16), b1 = v8 | (v9 << 16);
+                as_mma_bf16(c[i], ah[0], ah[1], ah[2], ah[3], b0, b1);
+                as_mma_bf16(c[i], am[0], am[1], am[2], am[3], b0, b1);
+                as_mma_bf16(c[i], al[0], al[1], al[2], al[3], b0, b1);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            const int nt = warp + 4 * i;
+            if (nt >= n_tiles) break;
+            const int col = nt * 8 + k0;
+            if (lower) {
+                float *dst = p.parts + (((long long)t * p.n_heads + kvh * group + row) * p.n_parts + part) * (vd + 2);
+                dst[col] = c[i][0], dst[col + 1] = c[i][1];
+            }
+            if (upper) {
+                float *dst = p.parts + (((long long)t * p.n_heads + kvh * group + row + 8) * p.n_parts + part) * (vd + 2);
+                dst[col] = c[i][2], dst[col + 1] = c[i][3];
+            }
+        }
+        if (tid < group) {
+            float *dst = p.parts + (((long long)t * p.n_heads + kvh * group + tid) * p.n_parts + part) * (vd + 2);
+#pragma unroll
+            for (int g = 0; g < GMAX; g++)
+                if (g == tid) dst[vd] = top[g];
+            dst[vd + 1] = (red[tid] + red[group + tid]) + (red[2 * group + tid] + red[3 * group + tid]);
+        }
+        return;
+    }
     // weighted values: a thread a value column (two for values beyond 128), every head of the group per value read
     float acc0[GMAX], acc1[GMAX];
 #pragma unroll
@@ -274,13 +379,13 @@ static int attention_split(int values_in_keys, const void *q, long long q_row, v
     const size_t smem = stage ? staged : small;
     cudaStream_t s = (cudaStream_t)stream;
     dim3 grid(n_tokens, n_kv_heads, p.n_parts), fold(n_tokens, n_heads);
-#define SPLIT_LAUNCH(T, STAGED, GMAX)                                                                     \
+#define SPLIT_LAUNCH(T, STAGED, GMAX, ...)                                                                \
     do {                                                                                                  \
         if (smem > 48 * 1024) {                                                                           \
-            cudaError_t e = abk_allow_shared_memory((const void *)attention_split_kernel<T, STAGED, GMAX>, (int)smem); \
+            cudaError_t e = abk_allow_shared_memory((const void *)attention_split_kernel<T, STAGED, GMAX, ##__VA_ARGS__>, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                          \
         }                                                                                                 \
-        abk_launch(attention_split_kernel<T, STAGED, GMAX>, grid, dim3(AS_THREADS), smem, s, p);         \
+        abk_launch(attention_split_kernel<T, STAGED, GMAX, ##__VA_ARGS__>, grid, dim3(AS_THREADS), smem, s, p);         \
     } while (0)
 #define SPLIT_BY_GROUP(T, STAGED)                   \
     do {                                            \
@@ -290,7 +395,11 @@ static int attention_split(int values_in_keys, const void *q, long long q_row, v
         else if (group <= 8) SPLIT_LAUNCH(T, STAGED, 8); \
         else SPLIT_LAUNCH(T, STAGED, 16);           \
     } while (0)
-    if (bf && stage) SPLIT_BY_GROUP(__nv_bfloat16, true);
+    const bool tensor = bf && stage && values_in_keys && head_dim % 16 == 0 && v_dim % 8 == 0 && v_dim <= 256;
+    if (tensor) {
+        if (group <= 8) SPLIT_LAUNCH(__nv_bfloat16, true, 8, true);
+        else SPLIT_LAUNCH(__nv_bfloat16, true, 16, true);
+    } else if (bf && stage) SPLIT_BY_GROUP(__nv_bfloat16, true);
     else if (bf) SPLIT_BY_GROUP(__nv_bfloat16, false);
     else if (stage) SPLIT_BY_GROUP(float, true);
     else SPLIT_BY_GROUP(float, false);
