@@ -4,7 +4,8 @@
 //   moe_route       per token: router logits z = R x in float32 (x as stored), the `top` largest (a tie goes to the
 //                   lower index), and each chosen expert's weight: sigmoid(z) (score 0) or its softmax over the
 //                   chosen (score 1). A pair is (token, k-th choice), numbered token * top + k; pairs of padding rows
-//                   carry expert -1.
+//                   carry expert -1. With `always` >= 0 every token has one more pair, its last: that expert with
+//                   weight 1 (a shared expert that lies stacked behind the routed ones).
 //   routed_product  out[pair] = act(W[expert of pair] (scale of pair * x[row of pair])): a product whose matrix is
 //                   chosen per row. With a scale the input is multiplied by it and rounded to its stored type first
 //                   (the weight acts on the expert's input). A CTA stages the pair's row in shared memory; a warp makes
@@ -18,17 +19,20 @@
 #define MR_THREADS 256
 template <typename T>
 __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T *x, long long ldx, const float *router, int d, int experts,
-                                                        int top, int softmax_chosen, const int *token_seq, int *pair_expert,
-                                                        float *pair_weight) {
+                                                        int top, int softmax_chosen, int always, const int *token_seq,
+                                                        int *pair_expert, float *pair_weight) {
     extern __shared__ __align__(16) float mr_smem[];  // [d, rounded up to 4] the row, [experts] logits, [experts] taken flags
     float *xs = mr_smem, *z = xs + ((d + 3) & ~3);
     int *taken = (int *)(z + experts);
     const int t = blockIdx.x, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int per = top + (always >= 0 ? 1 : 0);  // pairs a token has: its choices, then the expert every token uses
+    pair_expert += (long long)t * per, pair_weight += (long long)t * per;
     pdl_wait();
     if (token_seq[t] < 0) {
-        for (int k = tid; k < top; k += MR_THREADS) pair_expert[(long long)t * top + k] = -1, pair_weight[(long long)t * top + k] = 0.0f;
+        for (int k = tid; k < per; k += MR_THREADS) pair_expert[k] = -1, pair_weight[k] = 0.0f;
         return;
     }
+    if (always >= 0 && tid == 0) pair_expert[top] = always, pair_weight[top] = 1.0f;
     for (int i = tid; i < d; i += MR_THREADS) xs[i] = to_float(x[(long long)t * ldx + i]);
     for (int e = tid; e < experts; e += MR_THREADS) taken[e] = 0;
     __syncthreads();
@@ -57,21 +61,20 @@ __global__ void __launch_bounds__(MR_THREADS) moe_route_kernel(const T *x, long 
         denom += expf(best - chosen_max);
         if (lane == 0) {
             taken[at] = 1;
-            pair_expert[(long long)t * top + k] = at;
-            pair_weight[(long long)t * top + k] = softmax_chosen ? best : 1.0f / (1.0f + expf(-best));
+            pair_expert[k] = at;
+            pair_weight[k] = softmax_chosen ? best : 1.0f / (1.0f + expf(-best));
         }
         __syncwarp();
     }
     if (softmax_chosen && lane == 0)
         for (int k = 0; k < top; k++) {
-            float *w = pair_weight + (long long)t * top + k;
-            *w = expf(*w - chosen_max) / denom;
+            pair_weight[k] = expf(pair_weight[k] - chosen_max) / denom;
         }
 }
 
 extern "C" int abk_moe_route(const void *x, long long ldx, int dtype, const float *router, int n_tokens, int d, int experts,
-                             int top, int softmax_chosen, const int *token_seq, int *pair_expert, float *pair_weight,
-                             void *stream) {
+                             int top, int softmax_chosen, int always, const int *token_seq, int *pair_expert,
+                             float *pair_weight, void *stream) {
     if (n_tokens <= 0) return 0;
     if (top < 1 || top > experts) ABK_REFUSE("moe_route: %d of %d experts", top, experts);
     const size_t smem = (size_t)(((d + 3) & ~3) + 2 * experts) * 4;
@@ -83,14 +86,14 @@ extern "C" int abk_moe_route(const void *x, long long ldx, int dtype, const floa
             if (e != cudaSuccess) return (int)e;
         }
         abk_launch(moe_route_kernel<__nv_bfloat16>, dim3(n_tokens), dim3(MR_THREADS), smem, s, (const __nv_bfloat16 *)x, ldx, router,
-                   d, experts, top, softmax_chosen, token_seq, pair_expert, pair_weight);
+                   d, experts, top, softmax_chosen, always, token_seq, pair_expert, pair_weight);
     } else {
         if (smem > 48 * 1024) {
             cudaError_t e = abk_allow_shared_memory((const void *)moe_route_kernel<float>, (int)smem);
             if (e != cudaSuccess) return (int)e;
         }
         abk_launch(moe_route_kernel<float>, dim3(n_tokens), dim3(MR_THREADS), smem, s, (const float *)x, ldx, router, d, experts, top,
-                   softmax_chosen, token_seq, pair_expert, pair_weight);
+                   softmax_chosen, always, token_seq, pair_expert, pair_weight);
     }
     return ABK_LAUNCH_RESULT();
 }

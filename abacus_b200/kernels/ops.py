@@ -971,19 +971,21 @@ def gated_row_norm(o, gate, weight, out, eps, batch):
 RELU_SQUARED = 1
 
 
-def moe_route(x, router, top, batch, pair_expert, pair_weight, softmax_chosen=False):
+def moe_route(x, router, top, batch, pair_expert, pair_weight, softmax_chosen=False, always=None):
     """Per token the `top` experts with the largest router logits (router float32 [experts, d], x as stored) and their
     weights, sigmoid(logit) or the softmax over the chosen; pair token * top + k is the token's k-th choice
-    (pair_expert int32, -1 for padding rows; pair_weight float32)."""
+    (pair_expert int32, -1 for padding rows; pair_weight float32). always (an expert's index): every token has top + 1
+    pairs, the last that expert with weight 1."""
     _need_cuda(x, router, pair_expert, pair_weight)
     lib = load_module("moe")
     n, (experts, d) = batch.n_rows, router.shape
     assert router.dtype == torch.float32 and router.is_contiguous() and x.stride(1) == 1 and x.shape[1] == d
     assert pair_expert.dtype == torch.int32 and pair_weight.dtype == torch.float32
-    assert pair_expert.numel() >= n * top and pair_weight.numel() >= n * top
+    per = top + (0 if always is None else 1)
+    assert pair_expert.numel() >= n * per and pair_weight.numel() >= n * per
     _check(lib, lib.abk_moe_route(_p(x), _ll(x.stride(0)), _i(_dt(x)), _p(router), _i(n), _i(d), _i(experts), _i(top),
-                                  _i(1 if softmax_chosen else 0), _p(batch.token_seq), _p(pair_expert), _p(pair_weight),
-                                  _stream()), "moe_route")
+                                  _i(1 if softmax_chosen else 0), _i(-1 if always is None else always), _p(batch.token_seq),
+                                  _p(pair_expert), _p(pair_weight), _stream()), "moe_route")
 
 
 def routed_product(x, pairs_per_row, w, pair_expert, pair_scale, out, n_pairs, activation=0):

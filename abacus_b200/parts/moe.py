@@ -49,24 +49,36 @@ class RoutedMLP:
     def bind(self, params, ctx):
         s, self.ctx = self.spec, ctx
         self.router = to_device(params["router"], ctx, torch.float32)
-        self.up = to_device(torch.stack([params[f"up{e}"] for e in range(s.experts)]), ctx, ctx.dtype)
-        self.down = to_device(torch.stack([params[f"down{e}"] for e in range(s.experts)]), ctx, ctx.dtype)
+        ups, downs = [params[f"up{e}"] for e in range(s.experts)], [params[f"down{e}"] for e in range(s.experts)]
+        # a shared expert of the routed experts' own size and activation lies stacked behind them, and every token has
+        # one more pair: that expert, with weight 1 (no launches of its own; in a prompt it rides the grouped product)
+        self.stacked_shared = (s.shared is not None and s.shared.inter == s.expert.inter
+                               and s.shared.activation == s.expert.activation and s.weight_on == "input")
+        if self.stacked_shared:
+            ups, downs = ups + [params["shared_up"]], downs + [params["shared_down"]]
+        self.up = to_device(torch.stack(ups), ctx, ctx.dtype)
+        self.down = to_device(torch.stack(downs), ctx, ctx.dtype)
         self.shared_up = self.shared_down = None
-        if s.shared is not None:
+        if s.shared is not None and not self.stacked_shared:
             self.shared_up = Linear(to_device(params["shared_up"], ctx, ctx.dtype))
             self.shared_down = Linear(to_device(params["shared_down"], ctx, ctx.dtype))
 
     def step_weights(self):
         # of the experts a step reads only those its tokens chose; the router and the shared expert it reads whole
+        if self.stacked_shared:
+            return [self.router, self.up[self.spec.experts], self.down[self.spec.experts]]
         shared = [self.shared_up.weight, self.shared_down.weight] if self.shared_up is not None else []
         return [self.router, *shared]
 
     def forward(self, xn, out, batch, ws):
         s, n, dt = self.spec, batch.n_rows, self.ctx.dtype
-        pairs = n * s.top
+        top = s.top + (1 if self.stacked_shared else 0)   # pairs a token has
+        n_experts = s.experts + (1 if self.stacked_shared else 0)
+        pairs = n * top
         expert = ws.get("moe_expert", (pairs,), torch.int32)
         weight = ws.get("moe_weight", (pairs,), torch.float32)
-        ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen")
+        ops.moe_route(xn, self.router, s.top, batch, expert, weight, softmax_chosen=s.score == "softmax_chosen",
+                      always=s.experts if self.stacked_shared else None)
         on_input = s.weight_on == "input"
         if self.shared_up is not None:
             shared_act = ws.get("moe_shared_act", (n, s.shared.inter), dt)
@@ -74,23 +86,23 @@ class RoutedMLP:
             ops.relu_squared(shared_act, n)
             self.shared_down.forward(shared_act, out, n)
         if pairs > GROUPED_FROM and on_input and ops.grouped_takes(xn, self.up, self.down):
-            tiles = ops.grouped_tiles(pairs, s.experts)
+            tiles = ops.grouped_tiles(pairs, n_experts)
             rows = tiles * ops.GROUPED_ROWS
-            scratch = ws.get("moe_sort", (2 * s.experts + pairs,), torch.int32)
+            scratch = ws.get("moe_sort", (2 * n_experts + pairs,), torch.int32)
             place = ws.get("moe_place", (pairs,), torch.int32)
             tile_expert = ws.get("moe_tile_expert", (tiles,), torch.int32)
             sorted_rows = ws.get("moe_sorted", (rows, s.hidden), dt)
-            ops.moe_sort(xn, s.top, expert, weight, pairs, s.experts, scratch, place, tile_expert, sorted_rows)
+            ops.moe_sort(xn, top, expert, weight, pairs, n_experts, scratch, place, tile_expert, sorted_rows)
             act = ws.get("moe_act", (rows, s.expert.inter), dt)
             ops.gemm_grouped(sorted_rows, self.up, act, tile_expert, activation=_ACTIVATIONS[s.expert.activation])
             sorted_out = ws.get("moe_pair_out", (rows, s.hidden), torch.float32)
             ops.gemm_grouped(act, self.down, sorted_out, tile_expert)
-            ops.moe_unsort(sorted_out, place, out, n, s.top, add=self.shared_up is not None)
+            ops.moe_unsort(sorted_out, place, out, n, top, add=self.shared_up is not None)
             return out
         act = ws.get("moe_act", (pairs, s.expert.inter), dt)
-        ops.routed_product(xn, s.top, self.up, expert, weight if on_input else None, act, pairs,
+        ops.routed_product(xn, top, self.up, expert, weight if on_input else None, act, pairs,
                            activation=_ACTIVATIONS[s.expert.activation])
         pair_out = ws.get("moe_pair_out", (pairs, s.hidden), torch.float32)
         ops.routed_product(act, 1, self.down, expert, None if on_input else weight, pair_out, pairs)
-        ops.moe_combine(pair_out, out, n, s.top, add=self.shared_up is not None)
+        ops.moe_combine(pair_out, out, n, top, add=self.shared_up is not None)
         return out

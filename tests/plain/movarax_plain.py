@@ -179,7 +179,8 @@ def routed_feed_forward(h, p, mlp, rnd=None):
         for e, s in zip(chosen[t], scores[t]):
             out[t] += expert(_keep(rnd, h.dtype.type(s) * h[t:t + 1]), p[f"e{e}.up"], p[f"e{e}.down"], rnd)[0]
     if mlp.get("shared"):
-        out += expert(h, p["shared.up"], p["shared.down"], rnd, stored_before=True)
+        # (a shared expert of the routed experts' size runs with them; one of another size as products of its own)
+        out += expert(h, p["shared.up"], p["shared.down"], rnd, stored_before=mlp["shared"]["ff"] != mlp["expert"]["ff"])
     return out
 
 
