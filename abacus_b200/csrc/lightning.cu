@@ -170,6 +170,252 @@ extern "C" int abk_lightning_scan(const void *proj, long long ld, int dtype, int
     return ABK_LAUNCH_RESULT();
 }
 
+// ---------------------------------------------------------------- the same recurrence in chunks, for prompts
+// A sequence's tokens in chunks of 64. With a the head's decay, S the state before a chunk, i and j tokens of it:
+//     o_i = a^(i+1) S^T q_i + sum over j <= i of a^(i-j) (q_i . k_j) v_j,      S' = a^n S + sum_j a^(n-1-j) k_j v_j^T
+// so the chunks' own sums are made side by side (chunk_states), the states before every chunk follow from them in
+// one walk over whole matrices (chunk_prefix), and the outputs again side by side (chunk_outputs): what runs along
+// the sequence is one multiply-add a chunk and state value instead of a token's whole chain. All float32, on the
+// CUDA cores (scores and the state are float32 by the design's rule); sums are taken in another order than token by
+// token, within float32's rounding.
+#define LC_TOKENS 64
+#define LC_PITCH 68  // floats between rows of the transposed tiles (a multiple of 4 that is no multiple of 32)
+
+struct LightningChunks {
+    LightningScan s;
+    float *sums;   // [chunks][heads][dim][vdim]: a chunk's own sum, then (after the prefix) the state before it
+    int n_seqs, max_chunks;
+};
+
+// (sequence, chunk within it) of chunk number c in the step's order, or false beyond the last
+__device__ __forceinline__ bool chunk_of(const LightningChunks &p, int c, int &seq, int &chunk, int &first_chunk) {
+    int before = 0;
+    for (seq = 0; seq < p.n_seqs; seq++) {
+        const int n = p.s.seq_start[seq + 1] - p.s.seq_start[seq], nc = (n + LC_TOKENS - 1) / LC_TOKENS;
+        if (c < before + nc) {
+            chunk = c - before, first_chunk = before;
+            return true;
+        }
+        before += nc;
+    }
+    return false;
+}
+
+// sums[c][h][d][col] = sum_j a^(n-1-j) k_j[d] v_j[col] over the chunk's n tokens. A CTA: 128 channels x 128 columns,
+// a thread 8 x 8 of them.
+template <typename T> __global__ void __launch_bounds__(256) chunk_states_kernel(LightningChunks p, int v_tiles) {
+    extern __shared__ __align__(16) float lc_smem[];
+    float *k_s = lc_smem, *v_s = lc_smem + LC_TOKENS * 128;  // [64][128] each
+    const int c = blockIdx.x, h = blockIdx.y, d_tile = blockIdx.z / v_tiles, v_tile = blockIdx.z % v_tiles, tid = threadIdx.x;
+    const int dim = p.s.dim, vdim = p.s.vdim;
+    const float a = p.s.decay[h];
+    pdl_wait();
+    int seq, chunk, first;
+    if (!chunk_of(p, c, seq, chunk, first)) return;
+    const int row0 = p.s.seq_start[seq] + chunk * LC_TOKENS;
+    const int n = min(LC_TOKENS, p.s.seq_start[seq + 1] - row0);
+    const T *proj = (const T *)p.s.proj;
+    for (int e = tid; e < LC_TOKENS * 128; e += 256) {
+        const int j = e >> 7, x = e & 127, d = d_tile * 128 + x, col = v_tile * 128 + x;
+        float k = 0.0f, v = 0.0f;
+        if (j < n) {
+            const T *r = proj + (long long)(row0 + j) * p.s.ld;
+            if (d < dim) k = silu_staged<T>(to_float(r[p.s.k_at + (long long)h * dim + d])) * powf(a, (float)(n - 1 - j));
+            if (col < vdim) v = silu_staged<T>(to_float(r[p.s.v_at + (long long)h * vdim + col]));
+        }
+        k_s[e] = k, v_s[e] = v;
+    }
+    __syncthreads();
+    const int ty = tid >> 4, tx = tid & 15;
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int u = 0; u < 8; u++) acc[i][u] = 0.0f;
+    for (int j = 0; j < n; j++) {
+        const float4 k0 = *(const float4 *)(k_s + j * 128 + ty * 8), k1 = *(const float4 *)(k_s + j * 128 + ty * 8 + 4);
+        const float4 v0 = *(const float4 *)(v_s + j * 128 + tx * 8), v1 = *(const float4 *)(v_s + j * 128 + tx * 8 + 4);
+        const float kk[8] = {k0.x, k0.y, k0.z, k0.w, k1.x, k1.y, k1.z, k1.w}, vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int i = 0; i < 8; i++)
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc[i][u] = fmaf(kk[i], vv[u], acc[i][u]);
+    }
+    float *dst = p.sums + ((long long)c * p.s.n_heads + h) * dim * vdim;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int d = d_tile * 128 + ty * 8 + i;
+#pragma unroll
+        for (int u = 0; u < 8; u++) {
+            const int col = v_tile * 128 + tx * 8 + u;
+            if (d < dim && col < vdim) dst[(long long)d * vdim + col] = acc[i][u];
+        }
+    }
+}
+
+// Along a sequence: sums[c] becomes the state before chunk c, and the slot's state the one after the last chunk.
+__global__ void __launch_bounds__(256) chunk_prefix_kernel(LightningChunks p) {
+    const int seq = blockIdx.z, h = blockIdx.y;
+    const long long per_head = (long long)p.s.dim * p.s.vdim, e = (long long)blockIdx.x * 256 + threadIdx.x;
+    const float a = p.s.decay[h];
+    pdl_wait();
+    const int n = p.s.seq_start[seq + 1] - p.s.seq_start[seq];
+    if (n <= 0 || e >= per_head) return;
+    int first = 0;
+    for (int q = 0; q < seq; q++) first += (p.s.seq_start[q + 1] - p.s.seq_start[q] + LC_TOKENS - 1) / LC_TOKENS;
+    float *state = p.s.state + ((long long)p.s.seq_slot[seq] * p.s.n_heads + h) * per_head + e;
+    float s = *state;
+    const float full = powf(a, (float)LC_TOKENS);
+    for (int c = 0, left = n; left > 0; c++, left -= LC_TOKENS) {
+        float *at = p.sums + ((long long)(first + c) * p.s.n_heads + h) * per_head + e;
+        const float own = *at;
+        *at = s;
+        s = fmaf(left >= LC_TOKENS ? full : powf(a, (float)left), s, own);
+    }
+    *state = s;
+}
+
+// The chunk's outputs for 128 value columns. Shared memory: q and k transposed [channel][token], v [token][column],
+// the decayed causal scores transposed [j][i]. A thread: 4 x 4 scores, then 4 tokens x 8 columns of the output.
+template <typename T> __global__ void __launch_bounds__(256) chunk_outputs_kernel(LightningChunks p, int dim_pad) {
+    extern __shared__ __align__(16) float lc_smem[];
+    float *q_t = lc_smem, *k_t = q_t + dim_pad * LC_PITCH, *v_s = k_t + dim_pad * LC_PITCH;  // v_s [64][128]
+    float *p_t = v_s + LC_TOKENS * 128, *pw = p_t + LC_TOKENS * LC_PITCH;                     // pw[n] = a^n, n <= 64
+    const int c = blockIdx.x, h = blockIdx.y, v_tile = blockIdx.z, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
+    const int dim = p.s.dim, vdim = p.s.vdim;
+    const float a = p.s.decay[h];
+    pdl_wait();
+    int seq, chunk, first;
+    if (!chunk_of(p, c, seq, chunk, first)) return;
+    const int row0 = p.s.seq_start[seq] + chunk * LC_TOKENS;
+    const int n = min(LC_TOKENS, p.s.seq_start[seq + 1] - row0);
+    const T *proj = (const T *)p.s.proj;
+    if (tid <= LC_TOKENS) pw[tid] = powf(a, (float)tid);
+    for (int e = tid; e < LC_TOKENS * dim_pad; e += 256) {
+        const int j = e / dim_pad, d = e - j * dim_pad;
+        float q = 0.0f, k = 0.0f;
+        if (j < n && d < dim) {
+            const T *r = proj + (long long)(row0 + j) * p.s.ld + (long long)h * dim + d;
+            q = silu_staged<T>(to_float(r[p.s.q_at])), k = silu_staged<T>(to_float(r[p.s.k_at]));
+        }
+        q_t[d * LC_PITCH + j] = q, k_t[d * LC_PITCH + j] = k;
+    }
+    for (int e = tid; e < LC_TOKENS * 128; e += 256) {
+        const int j = e >> 7, col = v_tile * 128 + (e & 127);
+        v_s[e] = j < n && col < vdim
+            ? silu_staged<T>(to_float(proj[(long long)(row0 + j) * p.s.ld + p.s.v_at + (long long)h * vdim + col])) : 0.0f;
+    }
+    __syncthreads();
+    {   // scores: tokens i0..i0+3 against j0..j0+3, nothing above the diagonal
+        const int i0 = ty * 4, j0 = tx * 4;
+        float sc[4][4];
+#pragma unroll
+        for (int i = 0; i < 4; i++) sc[i][0] = sc[i][1] = sc[i][2] = sc[i][3] = 0.0f;
+        if (j0 <= i0 + 3) {
+            for (int d = 0; d < dim; d++) {
+                const float4 q = *(const float4 *)(q_t + d * LC_PITCH + i0), k = *(const float4 *)(k_t + d * LC_PITCH + j0);
+                const float qq[4] = {q.x, q.y, q.z, q.w}, kk[4] = {k.x, k.y, k.z, k.w};
+#pragma unroll
+                for (int i = 0; i < 4; i++)
+#pragma unroll
+                    for (int j = 0; j < 4; j++) sc[i][j] = fmaf(qq[i], kk[j], sc[i][j]);
+            }
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int j = 0; j < 4; j++)
+                p_t[(j0 + j) * LC_PITCH + i0 + i] = j0 + j <= i0 + i ? sc[i][j] * pw[i0 + i - j0 - j] : 0.0f;
+    }
+    __syncthreads();
+    const int i0 = ty * 4, c0 = tx * 8;
+    float acc[4][8];
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int u = 0; u < 8; u++) acc[i][u] = 0.0f;
+    // what the state before the chunk gives: q_i^T S, then a^(i+1) on it
+    const float *state = p.sums + ((long long)c * p.s.n_heads + h) * dim * vdim;
+    const int col0 = v_tile * 128 + c0;
+    const bool whole = col0 + 8 <= vdim && vdim % 4 == 0;
+    for (int d = 0; d < dim; d++) {
+        const float4 q = *(const float4 *)(q_t + d * LC_PITCH + i0);
+        const float qq[4] = {q.x, q.y, q.z, q.w};
+        float ss[8];
+        const float *sr = state + (long long)d * vdim + col0;
+        if (whole) {
+            const float4 s0 = *(const float4 *)sr, s1 = *(const float4 *)(sr + 4);
+            ss[0] = s0.x, ss[1] = s0.y, ss[2] = s0.z, ss[3] = s0.w, ss[4] = s1.x, ss[5] = s1.y, ss[6] = s1.z, ss[7] = s1.w;
+        } else {
+#pragma unroll
+            for (int u = 0; u < 8; u++) ss[u] = col0 + u < vdim ? sr[u] : 0.0f;
+        }
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc[i][u] = fmaf(qq[i], ss[u], acc[i][u]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++)
+#pragma unroll
+        for (int u = 0; u < 8; u++) acc[i][u] *= pw[i0 + i + 1];
+    // what the chunk's own tokens give
+    for (int j = 0; j < n; j++) {
+        const float4 w = *(const float4 *)(p_t + j * LC_PITCH + i0);
+        const float4 v0 = *(const float4 *)(v_s + j * 128 + c0), v1 = *(const float4 *)(v_s + j * 128 + c0 + 4);
+        const float ww[4] = {w.x, w.y, w.z, w.w}, vv[8] = {v0.x, v0.y, v0.z, v0.w, v1.x, v1.y, v1.z, v1.w};
+#pragma unroll
+        for (int i = 0; i < 4; i++)
+#pragma unroll
+            for (int u = 0; u < 8; u++) acc[i][u] = fmaf(ww[i], vv[u], acc[i][u]);
+    }
+#pragma unroll
+    for (int i = 0; i < 4; i++) {
+        if (i0 + i >= n) break;
+        float *dst = p.s.out + (long long)(row0 + i0 + i) * p.s.n_heads * vdim + (long long)h * vdim + col0;
+#pragma unroll
+        for (int u = 0; u < 8; u++)
+            if (col0 + u < vdim) dst[u] = acc[i][u];
+    }
+}
+
+// The recurrence of a step that brings prompts, in chunks of 64 tokens. sums: float32 scratch of at least
+// max_chunks * heads * dim * vdim, max_chunks >= ceil(tokens / 64) + sequences.
+extern "C" int abk_lightning_chunks(const void *proj, long long ld, int dtype, int q_at, int k_at, int v_at, int n_heads,
+                                    int dim, int vdim, const float *decay, float *state, float *out, const int *seq_start,
+                                    const int *seq_slot, int n_seqs, int max_chunks, float *sums, long long sums_floats,
+                                    void *stream) {
+    if (n_seqs <= 0 || max_chunks <= 0) return 0;
+    if (dim < 1 || dim > 256) ABK_REFUSE("lightning_chunks: %d key channels a head are not 1 to 256", dim);
+    if (vdim < 1 || n_heads < 1 || n_heads > 65535 || n_seqs > 65535)
+        ABK_REFUSE("lightning_chunks: %d heads of %d values, %d sequences", n_heads, vdim, n_seqs);
+    if ((long long)max_chunks * n_heads * dim * vdim > sums_floats)
+        ABK_REFUSE("lightning_chunks: the scratch memory holds %lld floats, the step needs %lld", sums_floats,
+                   (long long)max_chunks * n_heads * dim * vdim);
+    LightningChunks p;
+    p.s.proj = proj, p.s.ld = ld, p.s.q_at = q_at, p.s.k_at = k_at, p.s.v_at = v_at, p.s.n_heads = n_heads, p.s.dim = dim;
+    p.s.vdim = vdim, p.s.decay = decay, p.s.state = state, p.s.out = out, p.s.seq_start = seq_start, p.s.seq_slot = seq_slot;
+    p.sums = sums, p.n_seqs = n_seqs, p.max_chunks = max_chunks;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int d_tiles = (dim + 127) / 128, v_tiles = (vdim + 127) / 128, dim_pad = (dim + 3) & ~3;
+    const size_t smem_a = (size_t)2 * LC_TOKENS * 128 * 4;
+    const size_t smem_c = ((size_t)2 * dim_pad * LC_PITCH + LC_TOKENS * 128 + LC_TOKENS * LC_PITCH + LC_TOKENS + 4) * 4;
+    const long long per_head = (long long)dim * vdim;
+#define LC_LAUNCH(T)                                                                                                   \
+    do {                                                                                                               \
+        cudaError_t e = abk_allow_shared_memory((const void *)chunk_states_kernel<T>, (int)smem_a);                    \
+        if (e == cudaSuccess) e = abk_allow_shared_memory((const void *)chunk_outputs_kernel<T>, (int)smem_c);         \
+        if (e != cudaSuccess) return (int)e;                                                                           \
+        abk_launch(chunk_states_kernel<T>, dim3(max_chunks, n_heads, d_tiles * v_tiles), dim3(256), smem_a, s, p, v_tiles); \
+        abk_launch(chunk_prefix_kernel, dim3((unsigned)((per_head + 255) / 256), n_heads, n_seqs), dim3(256), 0, s, p); \
+        abk_launch(chunk_outputs_kernel<T>, dim3(max_chunks, n_heads, v_tiles), dim3(256), smem_c, s, p, dim_pad);     \
+    } while (0)
+    if (dtype == ABK_BF16) LC_LAUNCH(__nv_bfloat16);
+    else LC_LAUNCH(float);
+#undef LC_LAUNCH
+    return ABK_LAUNCH_RESULT();
+}
+
 // out[t] = w * o[t] / sqrt(mean(o[t]^2) + eps) * sigmoid(gate[t]); o float32 [tokens, width]; gate (the output type's)
 // at gate + t * ld_gate; rows of the step's padding (token_seq < 0) become zeros.
 template <typename T>

@@ -954,6 +954,28 @@ def lightning_scan(proj, q_at, k_at, v_at, n_heads, dim, vdim, decay, state, out
                                        _p(batch.seq_slot), _i(n_seqs), _stream()), "lightning_scan")
 
 
+LIGHTNING_CHUNK = 64  # tokens of a chunk of the chunked form
+
+
+def lightning_chunks(proj, q_at, k_at, v_at, n_heads, dim, vdim, decay, state, out, batch, ws):
+    """lightning_scan for steps that bring prompts: the same recurrence in chunks of 64 tokens, the chunks' sums and
+    outputs side by side and only the states between chunks along the sequence (csrc/lightning.cu). ws: a
+    parts.Workspace for the chunks' sums."""
+    _need_cuda(proj, decay, state, out)
+    lib = load_module("lightning")
+    n_seqs = batch.seq_slot.numel()
+    assert proj.stride(1) == 1 and proj.shape[0] >= batch.n_rows and out.dtype == torch.float32 and out.is_contiguous()
+    assert out.shape[1] == n_heads * vdim and decay.dtype == torch.float32 and decay.numel() == n_heads
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (n_heads, dim, vdim)
+    assert batch.seq_start.numel() >= n_seqs + 1
+    max_chunks = -(-batch.n_rows // LIGHTNING_CHUNK) + n_seqs
+    sums = ws.get("lightning_sums", (max_chunks * n_heads * dim * vdim,), torch.float32)
+    _check(lib, lib.abk_lightning_chunks(_p(proj), _ll(proj.stride(0)), _i(_dt(proj)), _i(q_at), _i(k_at), _i(v_at),
+                                         _i(n_heads), _i(dim), _i(vdim), _p(decay), _p(state), _p(out), _p(batch.seq_start),
+                                         _p(batch.seq_slot), _i(n_seqs), _i(max_chunks), _p(sums), _ll(sums.numel()),
+                                         _stream()), "lightning_chunks", kernels=3)
+
+
 def gated_row_norm(o, gate, weight, out, eps, batch):
     """out[t] = weight * o[t] / sqrt(mean(o[t]^2) + eps) * sigmoid(gate[t]) over a token's whole row; o float32
     [tokens, width], gate of out's type (rows of any pitch), weight float32 [width]; rows of padding become zeros."""

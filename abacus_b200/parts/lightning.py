@@ -69,8 +69,12 @@ class DecayAttention:
         proj = ws.get("decay_proj", (n, self.width), dt)
         self.in_proj.forward(xn, proj, n)
         o = ws.get("decay_o", (n, self.v_size), torch.float32)
-        ops.lightning_scan(proj, 0, self.at_k, self.at_v, s.n_heads, s.key_dim, s.value_dim, self.decay,
-                           cache.states["decay_state"], o, batch)
+        if batch.is_decode:  # a token a sequence: the recurrence as it stands
+            ops.lightning_scan(proj, 0, self.at_k, self.at_v, s.n_heads, s.key_dim, s.value_dim, self.decay,
+                               cache.states["decay_state"], o, batch)
+        else:  # prompts: in chunks of 64 tokens, only the states between chunks along the sequence
+            ops.lightning_chunks(proj, 0, self.at_k, self.at_v, s.n_heads, s.key_dim, s.value_dim, self.decay,
+                                 cache.states["decay_state"], o, batch, ws)
         normed = ws.get("decay_normed", (n, self.v_size), dt)
         ops.gated_row_norm(o, proj[:, self.at_g:], self.out_norm, normed, s.norm_eps, batch)
         self.o_proj.forward(normed, out, n)

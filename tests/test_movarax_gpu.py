@@ -154,17 +154,21 @@ def test_attention_over_latent_rows_finds_one_loud_key_wherever_it_is(dtype, H, 
         np.testing.assert_allclose(host(one)[1].reshape(H, R), want[-1], **tol)
 
 
+@pytest.mark.parametrize("form", ["token by token", "chunks"])
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,n,V", [(2, 5, 3), (3, 16, 8), (1, 40, 24), (2, 128, 70), (1, 200, 33)])
-def test_the_recurrence_whole_in_portions_token_by_token_and_in_an_unequal_batch(dtype, H, n, V):
+@pytest.mark.parametrize("H,n,V", [(2, 5, 3), (3, 16, 8), (1, 40, 24), (2, 128, 70), (1, 200, 133)])
+def test_the_recurrence_whole_in_portions_token_by_token_and_in_an_unequal_batch(dtype, H, n, V, form):
+    """Both kernels: the recurrence as it stands (decode steps) and in chunks of 64 tokens (steps that bring prompts)."""
     from abacus_b200.cache import CacheNeed, SequenceCache
     from abacus_b200.kernels import ops
+    from abacus_b200.parts import Workspace
+    ws = Workspace(torch.device(DEV, torch.cuda.current_device()))
     rng = np.random.default_rng(n)
     rnd = plain.bf16_round if dtype == "bfloat16" else (lambda a: a)
     decay = [0.999, 0.6, 1.0][:H]
     cache = SequenceCache([CacheNeed(states=(("decay_state", (H, n, V), "float32"),))], [None], 64, DT[dtype], DEV, max_slots=6)
     state = cache.views[0].states["decay_state"]
-    lens = [50, 1, 19]
+    lens = [150, 1, 70]
     at_k, at_v = H * n + 3, 2 * H * n + 8
     width = at_v + H * V + 1
     seqs = [rnd(rng.standard_normal((t, width)) * 1.5).astype(np.float32) for t in lens]
@@ -187,7 +191,10 @@ def test_the_recurrence_whole_in_portions_token_by_token_and_in_an_unequal_batch
             b = batch_of([(slots[i], z - a, a) for i, a, z in step])
             x = np.concatenate([seqs[i][a:z] for i, a, z in step])
             out = torch.empty((len(x), H * V), dtype=torch.float32, device=DEV)
-            ops.lightning_scan(dev(x, DT[dtype]), 0, at_k, at_v, H, n, V, dev(np.array(decay)), state, out, b)
+            if form == "chunks":
+                ops.lightning_chunks(dev(x, DT[dtype]), 0, at_k, at_v, H, n, V, dev(np.array(decay)), state, out, b, ws)
+            else:
+                ops.lightning_scan(dev(x, DT[dtype]), 0, at_k, at_v, H, n, V, dev(np.array(decay)), state, out, b)
             row = 0
             for i, a, z in step:
                 got[i].append(host(out[row:row + z - a]))
@@ -196,9 +203,9 @@ def test_the_recurrence_whole_in_portions_token_by_token_and_in_an_unequal_batch
             cache.close_slot(slot)
         return [np.concatenate(got[i]) for i in range(len(seqs))]
     state.fill_(3.0)   # a slot's state is zeroed when the slot is handed out, whatever its last user left
-    for what, steps in (("each whole, one batch", [[(0, 0, 50), (1, 0, 1), (2, 0, 19)]]),
-                        ("portions down to two tokens", [[(0, 0, 17), (2, 0, 2)], [(0, 17, 33), (1, 0, 1), (2, 2, 19)], [(0, 33, 35)], [(0, 35, 50)]]),
-                        ("token by token", [[(0, t, t + 1)] + ([(2, t, t + 1)] if t < 19 else []) + ([(1, 0, 1)] if t == 4 else []) for t in range(50)])):
+    for what, steps in (("each whole, one batch", [[(0, 0, 150), (1, 0, 1), (2, 0, 70)]]),
+                        ("portions down to two tokens", [[(0, 0, 67), (2, 0, 2)], [(0, 67, 131), (1, 0, 1), (2, 2, 70)], [(0, 131, 133)], [(0, 133, 150)]]),
+                        ("token by token", [[(0, t, t + 1)] + ([(2, t, t + 1)] if t < 70 else []) + ([(1, 0, 1)] if t == 4 else []) for t in range(150)])):
         for i, (g, w) in enumerate(zip(run(steps), want)):
             np.testing.assert_allclose(g, w, err_msg=f"{what}, sequence {i}", **tol)
 
