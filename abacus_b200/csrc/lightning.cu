@@ -206,6 +206,7 @@ __device__ __forceinline__ bool chunk_of(const LightningChunks &p, int c, int &s
 template <typename T> __global__ void __launch_bounds__(256) chunk_states_kernel(LightningChunks p, int v_tiles) {
     extern __shared__ __align__(16) float lc_smem[];
     float *k_s = lc_smem, *v_s = lc_smem + LC_TOKENS * 128;  // [64][128] each
+    __shared__ float pw[LC_TOKENS];                            // pw[m] = a^m
     const int c = blockIdx.x, h = blockIdx.y, d_tile = blockIdx.z / v_tiles, v_tile = blockIdx.z % v_tiles, tid = threadIdx.x;
     const int dim = p.s.dim, vdim = p.s.vdim;
     const float a = p.s.decay[h];
@@ -215,12 +216,14 @@ template <typename T> __global__ void __launch_bounds__(256) chunk_states_kernel
     const int row0 = p.s.seq_start[seq] + chunk * LC_TOKENS;
     const int n = min(LC_TOKENS, p.s.seq_start[seq + 1] - row0);
     const T *proj = (const T *)p.s.proj;
+    if (tid < LC_TOKENS) pw[tid] = powf(a, (float)tid);
+    __syncthreads();
     for (int e = tid; e < LC_TOKENS * 128; e += 256) {
         const int j = e >> 7, x = e & 127, d = d_tile * 128 + x, col = v_tile * 128 + x;
         float k = 0.0f, v = 0.0f;
         if (j < n) {
             const T *r = proj + (long long)(row0 + j) * p.s.ld;
-            if (d < dim) k = silu_staged<T>(to_float(r[p.s.k_at + (long long)h * dim + d])) * powf(a, (float)(n - 1 - j));
+            if (d < dim) k = silu_staged<T>(to_float(r[p.s.k_at + (long long)h * dim + d])) * pw[n - 1 - j];
             if (col < vdim) v = silu_staged<T>(to_float(r[p.s.v_at + (long long)h * vdim + col]));
         }
         k_s[e] = k, v_s[e] = v;
@@ -266,11 +269,20 @@ __global__ void __launch_bounds__(256) chunk_prefix_kernel(LightningChunks p) {
     float *state = p.s.state + ((long long)p.s.seq_slot[seq] * p.s.n_heads + h) * per_head + e;
     float s = *state;
     const float full = powf(a, (float)LC_TOKENS);
-    for (int c = 0, left = n; left > 0; c++, left -= LC_TOKENS) {
-        float *at = p.sums + ((long long)(first + c) * p.s.n_heads + h) * per_head + e;
-        const float own = *at;
-        *at = s;
-        s = fmaf(left >= LC_TOKENS ? full : powf(a, (float)left), s, own);
+    const int chunks = (n + LC_TOKENS - 1) / LC_TOKENS;
+    const long long step = (long long)p.s.n_heads * per_head;
+    float *at = p.sums + ((long long)first * p.s.n_heads + h) * per_head + e;
+    for (int c0 = 0; c0 < chunks; c0 += 8) {  // eight chunks' own sums are asked for together, then walked
+        float own[8];
+#pragma unroll
+        for (int i = 0; i < 8; i++) own[i] = c0 + i < chunks ? at[(c0 + i) * step] : 0.0f;
+#pragma unroll
+        for (int i = 0; i < 8; i++) {
+            if (c0 + i >= chunks) break;
+            const int left = n - (c0 + i) * LC_TOKENS;
+            at[(c0 + i) * step] = s;
+            s = fmaf(left >= LC_TOKENS ? full : powf(a, (float)left), s, own[i]);
+        }
     }
     *state = s;
 }
@@ -338,22 +350,30 @@ template <typename T> __global__ void __launch_bounds__(256) chunk_outputs_kerne
     const float *state = p.sums + ((long long)c * p.s.n_heads + h) * dim * vdim;
     const int col0 = v_tile * 128 + c0;
     const bool whole = col0 + 8 <= vdim && vdim % 4 == 0;
-    for (int d = 0; d < dim; d++) {
-        const float4 q = *(const float4 *)(q_t + d * LC_PITCH + i0);
-        const float qq[4] = {q.x, q.y, q.z, q.w};
-        float ss[8];
-        const float *sr = state + (long long)d * vdim + col0;
-        if (whole) {
-            const float4 s0 = *(const float4 *)sr, s1 = *(const float4 *)(sr + 4);
-            ss[0] = s0.x, ss[1] = s0.y, ss[2] = s0.z, ss[3] = s0.w, ss[4] = s1.x, ss[5] = s1.y, ss[6] = s1.z, ss[7] = s1.w;
-        } else {
+    for (int d0 = 0; d0 < dim; d0 += 4) {  // four channels' rows of the state are asked for together
+        float ss[4][8];
 #pragma unroll
-            for (int u = 0; u < 8; u++) ss[u] = col0 + u < vdim ? sr[u] : 0.0f;
+        for (int x = 0; x < 4; x++) {
+            const float *sr = state + (long long)(d0 + x < dim ? d0 + x : dim - 1) * vdim + col0;
+            if (whole) {
+                const float4 s0 = *(const float4 *)sr, s1 = *(const float4 *)(sr + 4);
+                ss[x][0] = s0.x, ss[x][1] = s0.y, ss[x][2] = s0.z, ss[x][3] = s0.w;
+                ss[x][4] = s1.x, ss[x][5] = s1.y, ss[x][6] = s1.z, ss[x][7] = s1.w;
+            } else {
+#pragma unroll
+                for (int u = 0; u < 8; u++) ss[x][u] = col0 + u < vdim ? sr[u] : 0.0f;
+            }
         }
 #pragma unroll
-        for (int i = 0; i < 4; i++)
+        for (int x = 0; x < 4; x++) {
+            // (channels beyond dim are rows of zeros in q_t: dim_pad is dim rounded up to 4)
+            const float4 q = *(const float4 *)(q_t + (d0 + x) * LC_PITCH + i0);
+            const float qq[4] = {q.x, q.y, q.z, q.w};
 #pragma unroll
-            for (int u = 0; u < 8; u++) acc[i][u] = fmaf(qq[i], ss[u], acc[i][u]);
+            for (int i = 0; i < 4; i++)
+#pragma unroll
+                for (int u = 0; u < 8; u++) acc[i][u] = fmaf(qq[i], ss[x][u], acc[i][u]);
+        }
     }
 #pragma unroll
     for (int i = 0; i < 4; i++)

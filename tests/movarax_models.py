@@ -53,8 +53,8 @@ CONFIGS = {
                      decay_layer("lightning", 2, 5, 3, (0.8, 1.0), dense(20)),
                      latent_layer(1, 12, 6, 20, 21, 0.3, rot=(100.0, 4), kv_from=0, mlp=experts(2, 2, 8, 8))]},
     "W": {"architecture": "Movarax", "vocab": 77, "width": 32, "norm": {"eps": 1e-5}, "embedding": {"scale": 0.25},
-          "layers": [latent_layer(2, 8, 8, 8, 16, 0.4, rot=(500000.0, 8), mlp=experts(1, 1, 8)),
-                     latent_layer(2, 8, 8, 8, 16, 0.4, rot=(500000.0, 8), mlp=dense(40)),
+          "layers": [latent_layer(2, 8, 8, 8, 16, 0.4, rot=(250000.0, 8), mlp=experts(1, 1, 8)),
+                     latent_layer(2, 8, 8, 8, 16, 0.4, rot=(250000.0, 8), mlp=dense(40)),
                      latent_layer(2, 4, 16, 8, 24, 0.3, rot=(50.0, 16))]},
 }
 
