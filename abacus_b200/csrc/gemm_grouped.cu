@@ -80,7 +80,21 @@ __global__ void __launch_bounds__(128) moe_gather_kernel(const __nv_bfloat16 *x,
     if (threadIdx.x == 0) place[p] = at;
     const __nv_bfloat16 *src = x + (long long)(p / pairs_per_row) * ldx;
     __nv_bfloat16 *dst = sorted + (long long)at * d;
-    if (pair_scale) {
+    if (d % 8 == 0 && ldx % 8 == 0 && (((uintptr_t)x | (uintptr_t)sorted) & 15) == 0) {  // 16-byte pieces
+        const float sc = pair_scale ? pair_scale[p] : 1.0f;
+        for (int i = threadIdx.x * 8; i < d; i += 128 * 8) {
+            uint4 raw = *(const uint4 *)(src + i);
+            if (pair_scale) {
+                __nv_bfloat162 *h = (__nv_bfloat162 *)&raw;
+#pragma unroll
+                for (int u = 0; u < 4; u++) {
+                    const float2 f = __bfloat1622float2(h[u]);
+                    h[u] = __floats2bfloat162_rn(sc * f.x, sc * f.y);
+                }
+            }
+            *(uint4 *)(dst + i) = raw;
+        }
+    } else if (pair_scale) {
         const float sc = pair_scale[p];
         for (int i = threadIdx.x; i < d; i += 128) dst[i] = __float2bfloat16_rn(sc * __bfloat162float(src[i]));
     } else {
@@ -283,29 +297,43 @@ extern "C" int abk_gemm_grouped(const void *x, const void *w, void *out, long lo
 }
 
 // ---------------------------------------------------------------- back to the tokens' order
-__global__ void __launch_bounds__(256) moe_unsort_kernel(const float *sorted, const int *place, float *out, long long total,
-                                                         int d, int top, int add) {
+// A CTA a token; VEC: four columns a thread as one 16-byte piece (d a multiple of 4).
+template <bool VEC>
+__global__ void __launch_bounds__(256) moe_unsort_kernel(const float *sorted, const int *place, float *out, int d, int top, int add) {
     pdl_wait();
-    const long long i = (long long)blockIdx.x * 256 + threadIdx.x;
-    if (i >= total) return;
-    const long long t = i / d, j = i - t * d;
-    float acc = 0.0f;
-    bool any = false;
-    for (int k = 0; k < top; k++) {
-        const int at = place[t * top + k];
-        if (at < 0) continue;
-        const float v = sorted[(long long)at * d + j];
-        acc = any ? acc + v : v;
-        any = true;
+    const long long t = blockIdx.x;
+    constexpr int W = VEC ? 4 : 1;
+    for (int j = threadIdx.x * W; j < d; j += 256 * W) {
+        float acc[W];
+        bool any = false;
+        for (int k = 0; k < top; k++) {
+            const int at = place[t * top + k];
+            if (at < 0) continue;
+            float v[W];
+            if (VEC) {
+                const float4 r = *(const float4 *)(sorted + (long long)at * d + j);
+                v[0] = r.x, v[W > 1 ? 1 : 0] = r.y, v[W > 2 ? 2 : 0] = r.z, v[W > 3 ? 3 : 0] = r.w;
+            } else {
+                v[0] = sorted[(long long)at * d + j];
+            }
+#pragma unroll
+            for (int u = 0; u < W; u++) acc[u] = any ? acc[u] + v[u] : v[u];
+            any = true;
+        }
+#pragma unroll
+        for (int u = 0; u < W; u++) {
+            const float a = any ? acc[u] : 0.0f;
+            out[t * d + j + u] = add ? out[t * d + j + u] + a : a;
+        }
     }
-    out[i] = add ? out[i] + acc : acc;
 }
 
 extern "C" int abk_moe_unsort(const float *sorted, const int *place, float *out, int n_tokens, int d, int top, int add,
                               void *stream) {
-    const long long total = (long long)n_tokens * d;
-    if (total <= 0) return 0;
-    abk_launch(moe_unsort_kernel, dim3((unsigned)((total + 255) / 256)), dim3(256), 0, (cudaStream_t)stream, sorted, place, out,
-               total, d, top, add);
+    if (n_tokens <= 0 || d <= 0) return 0;
+    if (d % 4 == 0 && (((uintptr_t)sorted | (uintptr_t)out) & 15) == 0)
+        abk_launch(moe_unsort_kernel<true>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, sorted, place, out, d, top, add);
+    else
+        abk_launch(moe_unsort_kernel<false>, dim3(n_tokens), dim3(256), 0, (cudaStream_t)stream, sorted, place, out, d, top, add);
     return ABK_LAUNCH_RESULT();
 }
