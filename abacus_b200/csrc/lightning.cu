@@ -288,11 +288,13 @@ __global__ void __launch_bounds__(256) chunk_prefix_kernel(LightningChunks p) {
 }
 
 // The chunk's outputs for 128 value columns. Shared memory: q and k transposed [channel][token], v [token][column],
-// the decayed causal scores transposed [j][i]. A thread: 4 x 4 scores, then 4 tokens x 8 columns of the output.
+// the decayed causal scores transposed [j][i] (where k was). A thread: 4 x 4 scores, then 4 tokens x 8 columns of the output.
 template <typename T> __global__ void __launch_bounds__(256) chunk_outputs_kernel(LightningChunks p, int dim_pad) {
     extern __shared__ __align__(16) float lc_smem[];
-    float *q_t = lc_smem, *k_t = q_t + dim_pad * LC_PITCH, *v_s = k_t + dim_pad * LC_PITCH;  // v_s [64][128]
-    float *p_t = v_s + LC_TOKENS * 128, *pw = p_t + LC_TOKENS * LC_PITCH;                     // pw[n] = a^n, n <= 64
+    // (the scores take k's place once every thread has made its own: two CTAs then share an SM)
+    const int k_rows = dim_pad > LC_TOKENS ? dim_pad : LC_TOKENS;
+    float *q_t = lc_smem, *k_t = q_t + dim_pad * LC_PITCH, *v_s = k_t + k_rows * LC_PITCH;  // v_s [64][128]
+    float *p_t = k_t, *pw = v_s + LC_TOKENS * 128;                                          // pw[n] = a^n, n <= 64
     const int c = blockIdx.x, h = blockIdx.y, v_tile = blockIdx.z, tid = threadIdx.x, ty = tid >> 4, tx = tid & 15;
     const int dim = p.s.dim, vdim = p.s.vdim;
     const float a = p.s.decay[h];
@@ -333,6 +335,7 @@ template <typename T> __global__ void __launch_bounds__(256) chunk_outputs_kerne
                     for (int j = 0; j < 4; j++) sc[i][j] = fmaf(qq[i], kk[j], sc[i][j]);
             }
         }
+        __syncthreads();  // every thread is done with k
 #pragma unroll
         for (int i = 0; i < 4; i++)
 #pragma unroll
@@ -419,7 +422,7 @@ extern "C" int abk_lightning_chunks(const void *proj, long long ld, int dtype, i
     cudaStream_t s = (cudaStream_t)stream;
     const int d_tiles = (dim + 127) / 128, v_tiles = (vdim + 127) / 128, dim_pad = (dim + 3) & ~3;
     const size_t smem_a = (size_t)2 * LC_TOKENS * 128 * 4;
-    const size_t smem_c = ((size_t)2 * dim_pad * LC_PITCH + LC_TOKENS * 128 + LC_TOKENS * LC_PITCH + LC_TOKENS + 4) * 4;
+    const size_t smem_c = ((size_t)(dim_pad + (dim_pad > LC_TOKENS ? dim_pad : LC_TOKENS)) * LC_PITCH + LC_TOKENS * 128 + LC_TOKENS + 4) * 4;
     const long long per_head = (long long)dim * vdim;
 #define LC_LAUNCH(T)                                                                                                   \
     do {                                                                                                               \
