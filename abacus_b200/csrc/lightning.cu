@@ -94,6 +94,7 @@ template <typename T, int DPT, int PARTS, int COLS> __global__ void __launch_bou
         for (int it = 0; it < PER; it++) {
             // (every load is made, from a place that exists, and dropped where it is not wanted: loads that hang on no
             // branch are all in flight together)
+            if (it * THREADS >= cnt * DP) break;  // (the same for every thread: the chunk has no such token)
             const int e = tid + it * THREADS, tok = e / DP, d = e % DP;
             const bool in = tok < cnt && d < p.dim;
             const T *r = proj + (long long)(row0 + c0 + (tok < cnt ? tok : cnt - 1)) * p.ld + (long long)h * p.dim + (d < p.dim ? d : 0);
@@ -102,6 +103,7 @@ template <typename T, int DPT, int PARTS, int COLS> __global__ void __launch_bou
         }
 #pragma unroll
         for (int it = 0; it < PER_V; it++) {
+            if (it * THREADS >= cnt * COLS) break;
             const int e = tid + it * THREADS, tok = e / COLS, c = tile * COLS + e % COLS;
             const float v = to_float(proj[(long long)(row0 + c0 + (tok < cnt ? tok : cnt - 1)) * p.ld + p.v_at + (long long)h * p.vdim +
                                           (c < p.vdim ? c : 0)]);
@@ -114,13 +116,14 @@ template <typename T, int DPT, int PARTS, int COLS> __global__ void __launch_bou
         __syncthreads();  // the chunk before is done with
 #pragma unroll
         for (int it = 0; it < PER; it++) {
+            if (it * THREADS >= cnt * DP) break;
             const int e = tid + it * THREADS, tok = e / DP, d = e % DP, at = (d / DPT) * (DPT + 4) + d % DPT;
             q_s[tok][at] = silu_staged<T>(rq[it]), k_s[tok][at] = silu_staged<T>(rk[it]);
         }
 #pragma unroll
         for (int it = 0; it < PER_V; it++) {
             const int e = tid + it * THREADS;
-            if (e < LS_TOKENS * COLS) v_s[e / COLS][e % COLS] = silu_staged<T>(rv[it]);
+            if (e < cnt * COLS) v_s[e / COLS][e % COLS] = silu_staged<T>(rv[it]);
         }
         __syncthreads();
         if (c0 + LS_TOKENS < n) fetch(c0 + LS_TOKENS);
