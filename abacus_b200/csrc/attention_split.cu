@@ -381,7 +381,7 @@ static int attention_split(int values_in_keys, const void *q, long long q_row, v
     dim3 grid(n_tokens, n_kv_heads, p.n_parts), fold(n_tokens, n_heads);
 #define SPLIT_LAUNCH(T, STAGED, GMAX, ...)                                                                \
     do {                                                                                                  \
-        if (smem > 48 * 1024) {                                                                           \
+        if (smem + 4096 > 48 * 1024) { /* (the kernel's own 2 KB of static shared memory count too) */    \
             cudaError_t e = abk_allow_shared_memory((const void *)attention_split_kernel<T, STAGED, GMAX, ##__VA_ARGS__>, (int)smem); \
             if (e != cudaSuccess) return (int)e;                                                          \
         }                                                                                                 \
