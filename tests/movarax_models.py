@@ -59,6 +59,45 @@ CONFIGS = {
 }
 
 
+def random_config(rng):
+    """A random configuration: two to five layers of either mixer, heads of 1 to 32, sizes that fit and that do not fit
+    the vector kernels, rotations of part or none of the rotated part, layers that read an earlier layer's latents, every
+    kind of feed-forward or none."""
+    width = int(rng.choice([24, 32, 40, 64, 72, 96, 128]))
+    n_layers = int(rng.integers(2, 6))
+    layers, latent_at = [], []
+    for i in range(n_layers):
+        kind = rng.choice(['latent', 'decay'])
+        r = rng.random()
+        if r < 0.25: mlp = None
+        elif r < 0.5: mlp = dense(int(rng.choice([16, 24, 40, 64])))
+        else:
+            E = int(rng.choice([1, 2, 3, 4, 8, 16])); top = int(rng.integers(1, min(E, 4) + 1)); ff = int(rng.choice([8, 12, 16, 24, 32]))
+            shared = None if rng.random() < 0.3 else (ff if rng.random() < 0.6 else int(rng.choice([8, 16, 20])))
+            mlp = experts(E, top, ff, shared)
+        if kind == 'latent':
+            own = [j for j in latent_at if 'kv_from' not in layers[j]['mixer']]
+            if own and rng.random() < 0.4:
+                j = int(rng.choice(own)); src = layers[j]['mixer']
+                H = int(rng.choice([1, 2, 3, 4, 8, 17, 24])); dim = int(rng.choice([1, 4, 8, 12, 16, 32])); vdim = int(rng.choice([3, 8, 16, 24, 40]))
+                rot = (src['rot']['base'], src['rot']['dims']) if 'rot' in src else None
+                layers.append(latent_layer(H, dim, src['rot_dim'], vdim, src['kv_rank'], 0.3, rot=rot, kv_from=j, mlp=mlp))
+            else:
+                H = int(rng.choice([1, 2, 3, 4, 8, 17, 24, 32])); dim = int(rng.choice([1, 4, 8, 12, 16, 32, 64]))
+                rot_dim = int(rng.choice([0, 2, 4, 8, 16, 32])); vdim = int(rng.choice([3, 8, 16, 24, 40, 136]))
+                rank = int(rng.choice([5, 8, 16, 24, 32, 48, 96, 160]))
+                dims = int(rng.choice([d for d in (0, 2, 4, 8, 16, 32) if d <= rot_dim]))
+                rot = (float(rng.choice([100.0, 10000.0, 1e6])), dims) if dims else None
+                layers.append(latent_layer(H, dim, rot_dim, vdim, rank, float(rng.choice([0.2, 0.35, 0.5])), rot=rot, mlp=mlp))
+            latent_at.append(i)
+        else:
+            H = int(rng.choice([1, 2, 3, 5, 8])); dim = int(rng.choice([1, 5, 16, 24, 64, 100, 128, 130])); vdim = int(rng.choice([1, 3, 8, 20, 32, 130]))
+            decay = [float(x) for x in rng.choice([0.0, 0.3, 0.9, 0.99, 0.999, 1.0], H)]
+            layers.append(decay_layer(str(rng.choice(['lightning', 'lightning_2'])), H, dim, vdim, decay, mlp))
+    return {"architecture": "Movarax", "vocab": int(rng.choice([50, 131, 300])), "width": width, "norm": {"eps": float(rng.choice([1e-6, 1e-5]))},
+            "embedding": {"scale": float(rng.choice([0.5, 1.0, 3.0]))}, "layers": layers}
+
+
 def config(name):
     return json.loads(json.dumps(CONFIGS[name]))
 
