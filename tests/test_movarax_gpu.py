@@ -114,7 +114,7 @@ def _latent_attention_want(q, rows, R, scale, sink):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("H,row,R", [(2, 24, 16), (5, 112, 96), (20, 40, 33), (16, 64, 48), (32, 96, 80), (3, 168, 160)])
+@pytest.mark.parametrize("H,row,R", [(2, 24, 16), (5, 112, 96), (20, 40, 33), (16, 64, 48), (32, 96, 80), (3, 168, 160), (8, 256, 192)])
 def test_attention_over_latent_rows_finds_one_loud_key_wherever_it_is(dtype, H, row, R):
     """A query that matches one key far more than the others: far back, at the sequence's start, on both sides of page
     borders, the token itself; the prompt in one step, and a token alone against a cache in a slot that was used before."""
